@@ -3,8 +3,10 @@
 //
 //   q_h <- rotate(rms_norm(q_h) * wq),  k_g <- rotate(rms_norm(k_g) * wk)       (norm weights shared by the heads)
 //
-// rotate turns the first `rot_dims` entries of a head pair by pair, entry 2i with entry 2i + 1, by
-// the angle position * inv_freq[i], cos and sin multiplied by `mag`; the other entries pass.  q goes
+// rotate turns the first `rot_dims` entries of a head pair by pair, entry 2i with entry 2i + 1 (or, with
+// `halves`, entry i with entry i + rot_dims / 2), by the angle position * inv_freq[i], cos and sin
+// multiplied by `mag`; the other entries pass.  With `maps` > 1 a head is that many units side by side
+// (the maps of differential attention), each normed and turned by itself; the values belong to the head.  q goes
 // to its buffer, k into the request's cache page, and the values - a projection of their own, or
 // the keys as projected, before norm and rotation - beside it.  Grid (token, share of the token's heads).  Norm, angle and rotation are float32.
 // Also here: the sigmoid gate on a mixer's output.
@@ -19,33 +21,37 @@ template <typename T, typename TW>
 __global__ void __launch_bounds__(PREP_WARPS * 32)
 headnorm_rope_cache_kernel(const T* __restrict__ u, long long u_stride, int q_col, int k_col, int v_col,
                            const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w, float eps,
-                           const float* __restrict__ inv_freq, int rot_dims, float mag, T* __restrict__ q_out,
-                           PagedCache cache, int v_dim, const int32_t* __restrict__ positions,
+                           const float* __restrict__ inv_freq, int rot_dims, int halves, int maps, float mag,
+                           T* __restrict__ q_out, PagedCache cache, int v_dim, const int32_t* __restrict__ positions,
                            const int32_t* __restrict__ row_seq, int q_heads, int write_cache) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float head_smem[];  // PREP_WARPS * head_dim
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x, d = cache.head_dim;
+  const int t = blockIdx.x, d = cache.head_dim / maps;      // a head holds `maps` units, each normed and turned by itself
   float* s = head_smem + warp * d;
   const int pos = positions[t], seq = row_seq[t];
   const T* row = u + (long long)t * u_stride;
-  for (int item = blockIdx.y * PREP_WARPS + warp; item < q_heads + cache.kv_heads; item += gridDim.y * PREP_WARPS) {
-    const bool is_q = item < q_heads;
-    const int h = is_q ? item : item - q_heads;
-    const T* x = row + (is_q ? q_col : k_col) + h * d;
+  const int units = (q_heads + cache.kv_heads) * maps;
+  for (int item = blockIdx.y * PREP_WARPS + warp; item < units; item += gridDim.y * PREP_WARPS) {
+    const bool is_q = item < q_heads * maps;
+    const int unit = is_q ? item : item - q_heads * maps;
+    const int h = unit / maps, map = unit - h * maps;
+    const T* x = row + (is_q ? q_col : k_col) + (long long)unit * d;
     const TW* w = is_q ? q_norm_w : k_norm_w;
     T* dst = nullptr;
     if (is_q) {
-      dst = q_out + ((long long)t * q_heads + h) * d;
+      dst = q_out + ((long long)t * q_heads * maps + unit) * d;
     } else if (write_cache) {
       const int page = cache.block_table[(long long)seq * cache.table_stride + pos / cache.page_tokens];
       if (page >= 0) {
         const long long slot = (long long)h * cache.page_tokens + (pos % cache.page_tokens);
-        dst = (T*)cache.k + (long long)page * cache.page_stride + slot * d;
-        T* vdst = (T*)cache.v + (long long)page * cache.page_stride + slot * v_dim;
-        const T* vx = v_col >= 0 ? row + v_col + h * v_dim : x;
-        for (int c = lane; c < v_dim; c += 32) vdst[c] = vx[c];
+        dst = (T*)cache.k + (long long)page * cache.page_stride + slot * cache.head_dim + map * d;
+        if (map == 0) {
+          T* vdst = (T*)cache.v + (long long)page * cache.page_stride + slot * v_dim;
+          const T* vx = v_col >= 0 ? row + v_col + h * v_dim : x;
+          for (int c = lane; c < v_dim; c += 32) vdst[c] = vx[c];
+        }
       }
     }
     if (!dst) continue;      // the whole warp takes the same way
@@ -57,15 +63,17 @@ headnorm_rope_cache_kernel(const T* __restrict__ u, long long u_stride, int q_co
     }
     const float scale = w ? 1.0f / sqrtf(warp_sum(sq) / (float)d + eps) : 1.0f;
     __syncwarp();
-    for (int p = lane; p < rot_dims / 2; p += 32) {
+    const int half = rot_dims / 2;
+    for (int p = lane; p < half; p += 32) {
       float sn, cs;
       sincosf((float)pos * inv_freq[p], &sn, &cs);
       sn *= mag;
       cs *= mag;
-      const float a = s[2 * p] * scale * (w ? to_float(w[2 * p]) : 1.0f);
-      const float b = s[2 * p + 1] * scale * (w ? to_float(w[2 * p + 1]) : 1.0f);
-      dst[2 * p] = from_float<T>(a * cs - b * sn);
-      dst[2 * p + 1] = from_float<T>(b * cs + a * sn);
+      const int ia = halves ? p : 2 * p, ib = halves ? p + half : 2 * p + 1;
+      const float a = s[ia] * scale * (w ? to_float(w[ia]) : 1.0f);
+      const float b = s[ib] * scale * (w ? to_float(w[ib]) : 1.0f);
+      dst[ia] = from_float<T>(a * cs - b * sn);
+      dst[ib] = from_float<T>(b * cs + a * sn);
     }
     for (int c = rot_dims + lane; c < d; c += 32) dst[c] = from_float<T>(s[c] * scale * (w ? to_float(w[c]) : 1.0f));
     __syncwarp();
@@ -75,28 +83,30 @@ headnorm_rope_cache_kernel(const T* __restrict__ u, long long u_stride, int q_co
 // dtype: element type of u, q_out, the cache and the norm weights.
 extern "C" int llm_headnorm_rope_cache(const void* u, int dtype, long long u_stride, int q_col, int k_col, int v_col,
                                        const void* q_norm_w, const void* k_norm_w, float eps, const float* inv_freq,
-                                       int rot_dims, float mag, void* q_out, void* k_base, void* v_base,
+                                       int rot_dims, int halves, int maps, float mag, void* q_out, void* k_base,
+                                       void* v_base,
                                        const int32_t* block_table, long long page_stride, int table_stride,
                                        int page_tokens, int kv_heads, int head_dim, int v_dim, const int32_t* positions,
                                        const int32_t* row_seq, int q_heads, int write_cache, int n_tokens,
                                        cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  LLM_HOST_CHECK(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= head_dim && (rot_dims == 0 || inv_freq), ERR_BAD_SIZE);
-  LLM_HOST_CHECK(v_col >= 0 || v_dim == head_dim, ERR_BAD_SIZE);
+  LLM_HOST_CHECK(maps >= 1 && head_dim % maps == 0, ERR_BAD_SIZE);
+  LLM_HOST_CHECK(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= head_dim / maps && (rot_dims == 0 || inv_freq), ERR_BAD_SIZE);
+  LLM_HOST_CHECK(v_col >= 0 || (v_dim == head_dim && maps == 1), ERR_BAD_SIZE);
   const size_t smem = (size_t)PREP_WARPS * head_dim * sizeof(float);
   LLM_HOST_CHECK(smem <= 48 * 1024, ERR_BAD_SIZE);
   PagedCache c{k_base, v_base, block_table, page_stride, table_stride, page_tokens, kv_heads, head_dim};
   // few tokens: a token's heads are dealt to several blocks, so that the step still fills the GPU
-  const int per_token = n_tokens >= 256 ? 1 : min((q_heads + kv_heads + PREP_WARPS - 1) / PREP_WARPS, 16);
+  const int per_token = n_tokens >= 256 ? 1 : min(((q_heads + kv_heads) * maps + PREP_WARPS - 1) / PREP_WARPS, 16);
   const dim3 grid(n_tokens, per_token);
   if (dtype == DT_F32)
     launch_kernel(headnorm_rope_cache_kernel<float, float>, grid, PREP_WARPS * 32, smem, stream, (const float*)u,
                   u_stride, q_col, k_col, v_col, (const float*)q_norm_w, (const float*)k_norm_w, eps, inv_freq, rot_dims,
-                  mag, (float*)q_out, c, v_dim, positions, row_seq, q_heads, write_cache);
+                  halves, maps, mag, (float*)q_out, c, v_dim, positions, row_seq, q_heads, write_cache);
   else if (dtype == DT_BF16)
     launch_kernel(headnorm_rope_cache_kernel<__nv_bfloat16, __nv_bfloat16>, grid, PREP_WARPS * 32, smem, stream,
                   (const __nv_bfloat16*)u, u_stride, q_col, k_col, v_col, (const __nv_bfloat16*)q_norm_w,
-                  (const __nv_bfloat16*)k_norm_w, eps, inv_freq, rot_dims, mag, (__nv_bfloat16*)q_out, c, v_dim,
+                  (const __nv_bfloat16*)k_norm_w, eps, inv_freq, rot_dims, halves, maps, mag, (__nv_bfloat16*)q_out, c, v_dim,
                   positions, row_seq, q_heads, write_cache);
   else
     return ERR_BAD_DTYPE;

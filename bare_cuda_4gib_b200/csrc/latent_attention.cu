@@ -23,13 +23,16 @@
 
 // ------------------------------------------------------------------------------ prepare
 
-// One block per token.  u holds the token's projections: the queries at q_col (per head `dim` plain
-// entries, then `rot`), the compressed row at c_col (`rank` entries to norm, then `rot`).
+// One block per token.  u holds the token's queries at q_col (per head `dim` plain entries, then
+// `rot`), c_src its compressed row (`rank` entries to norm, then `rot`; null where the run reads a
+// cache that another run wrote).  Rotated entries are paired (2i, 2i + 1), or with `halves`
+// (i, i + rot_dims / 2).
 template <typename T, typename TW>
 __global__ void __launch_bounds__(LAT_THREADS)
-latent_prepare_kernel(const T* __restrict__ u, long long u_stride, int q_col, int c_col, int heads, int dim, int rot,
+latent_prepare_kernel(const T* __restrict__ u, long long u_stride, int q_col, const T* __restrict__ c_src,
+                      long long c_stride, int heads, int dim, int rot,
                       int rank, const TW* __restrict__ norm_w, float eps, const float* __restrict__ inv_freq,
-                      int rot_dims, float mag, T* __restrict__ q_full, PagedCache cache,
+                      int rot_dims, int halves, float mag, T* __restrict__ q_full, PagedCache cache,
                       const int32_t* __restrict__ positions, const int32_t* __restrict__ row_seq, int write_cache) {
   pdl_launch_dependents();
   pdl_wait();
@@ -47,24 +50,25 @@ latent_prepare_kernel(const T* __restrict__ u, long long u_stride, int q_col, in
     sn *= mag;
     cs *= mag;
     const T* x = row + q_col + (long long)h * (dim + rot) + dim;
-    const float a = to_float(x[2 * p]), b = to_float(x[2 * p + 1]);
+    const int ia = halves ? p : 2 * p, ib = halves ? p + half : 2 * p + 1;
+    const float a = to_float(x[ia]), b = to_float(x[ib]);
     T* dst = q_full + ((long long)t * heads + h) * D + rank;
-    dst[2 * p] = from_float<T>(a * cs - b * sn);
-    dst[2 * p + 1] = from_float<T>(b * cs + a * sn);
+    dst[ia] = from_float<T>(a * cs - b * sn);
+    dst[ib] = from_float<T>(b * cs + a * sn);
   }
   for (int i = threadIdx.x; i < heads * (rot - rot_dims); i += blockDim.x) {
     const int h = i / (rot - rot_dims), c = rot_dims + i - h * (rot - rot_dims);
     q_full[((long long)t * heads + h) * D + rank + c] = row[q_col + (long long)h * (dim + rot) + dim + c];
   }
-  // the latent and the shared rotated key part
-  const T* x = row + c_col;
+  // the latent and the shared rotated key part (a run that reads another run's cache has neither)
+  if (!write_cache || !c_src) return;
+  const T* x = c_src + (long long)t * c_stride;
   float sq = 0.0f;
   for (int i = threadIdx.x; i < rank; i += blockDim.x) {
     const float v = to_float(x[i]);
     sq += v * v;
   }
   const float scale = 1.0f / sqrtf(block_sum(sq, scratch) / (float)rank + eps);
-  if (!write_cache) return;
   const long long off = cache_offset(cache, seq, pos, 0);
   if (off < 0) return;
   T* dst = (T*)cache.k + off;
@@ -74,29 +78,71 @@ latent_prepare_kernel(const T* __restrict__ u, long long u_stride, int q_col, in
     sincosf((float)pos * inv_freq[p], &sn, &cs);
     sn *= mag;
     cs *= mag;
-    const float a = to_float(x[rank + 2 * p]), b = to_float(x[rank + 2 * p + 1]);
-    dst[rank + 2 * p] = from_float<T>(a * cs - b * sn);
-    dst[rank + 2 * p + 1] = from_float<T>(b * cs + a * sn);
+    const int ia = rank + (halves ? p : 2 * p), ib = rank + (halves ? p + half : 2 * p + 1);
+    const float a = to_float(x[ia]), b = to_float(x[ib]);
+    dst[ia] = from_float<T>(a * cs - b * sn);
+    dst[ib] = from_float<T>(b * cs + a * sn);
   }
   for (int c = rot_dims + threadIdx.x; c < rot; c += blockDim.x) dst[rank + c] = x[rank + c];
 }
 
-extern "C" int llm_latent_prepare(const void* u, int dtype, long long u_stride, int q_col, int c_col, int heads, int dim,
+extern "C" int llm_latent_prepare(const void* u, int dtype, long long u_stride, int q_col, const void* c_src,
+                                  long long c_stride, int heads, int dim,
                                   int rot, int rank, const void* norm_w, float eps, const float* inv_freq, int rot_dims,
-                                  float mag, void* q_full, void* k_base, const int32_t* block_table, long long page_stride,
-                                  int table_stride, int page_tokens, const int32_t* positions, const int32_t* row_seq,
-                                  int write_cache, int n_tokens, cudaStream_t stream) {
+                                  int halves, float mag, void* q_full, void* k_base, const int32_t* block_table,
+                                  long long page_stride, int table_stride, int page_tokens, const int32_t* positions,
+                                  const int32_t* row_seq, int write_cache, int n_tokens, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   LLM_HOST_CHECK(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= rot && (rot_dims == 0 || inv_freq), ERR_BAD_SIZE);
+  LLM_HOST_CHECK(!write_cache || (c_src && norm_w), ERR_BAD_SIZE);
   PagedCache c{k_base, k_base, block_table, page_stride, table_stride, page_tokens, 1, rank + rot};
   if (dtype == DT_F32)
     launch_kernel(latent_prepare_kernel<float, float>, n_tokens, LAT_THREADS, 0, stream, (const float*)u, u_stride,
-                  q_col, c_col, heads, dim, rot, rank, (const float*)norm_w, eps, inv_freq, rot_dims, mag,
-                  (float*)q_full, c, positions, row_seq, write_cache);
+                  q_col, (const float*)c_src, c_stride, heads, dim, rot, rank, (const float*)norm_w, eps, inv_freq,
+                  rot_dims, halves, mag, (float*)q_full, c, positions, row_seq, write_cache);
   else if (dtype == DT_BF16)
     launch_kernel(latent_prepare_kernel<__nv_bfloat16, __nv_bfloat16>, n_tokens, LAT_THREADS, 0, stream,
-                  (const __nv_bfloat16*)u, u_stride, q_col, c_col, heads, dim, rot, rank, (const __nv_bfloat16*)norm_w,
-                  eps, inv_freq, rot_dims, mag, (__nv_bfloat16*)q_full, c, positions, row_seq, write_cache);
+                  (const __nv_bfloat16*)u, u_stride, q_col, (const __nv_bfloat16*)c_src, c_stride, heads, dim, rot, rank,
+                  (const __nv_bfloat16*)norm_w, eps, inv_freq, rot_dims, halves, mag, (__nv_bfloat16*)q_full, c,
+                  positions, row_seq, write_cache);
+  else
+    return ERR_BAD_DTYPE;
+  return launch_status();
+}
+
+// ------------------------------------------------------------------------------ norm of a latent
+
+// out[t, :] = x[t, :] / sqrt(mean(x[t, :]^2) + eps) * w: the norm of a compressed row that a product
+// follows (queries that go through a latent of their own).  x may be a column view; a warp per row.
+template <typename T, typename TW>
+__global__ void __launch_bounds__(128)
+rows_rmsnorm_kernel(const T* __restrict__ x, long long x_stride, const TW* __restrict__ w, T* __restrict__ out,
+                    long long out_stride, int rows, int width, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (r >= rows) return;
+  const T* xr = x + (long long)r * x_stride;
+  float sq = 0.0f;
+  for (int c = lane; c < width; c += 32) {
+    const float v = to_float(xr[c]);
+    sq += v * v;
+  }
+  const float scale = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+  for (int c = lane; c < width; c += 32)
+    out[(long long)r * out_stride + c] = from_float<T>(to_float(xr[c]) * scale * to_float(w[c]));
+}
+
+extern "C" int llm_rows_rmsnorm(const void* x, long long x_stride, const void* w, void* out, long long out_stride,
+                                int dtype, int rows, int width, float eps, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  const int blocks = (rows + 3) / 4;
+  if (dtype == DT_F32)
+    launch_kernel(rows_rmsnorm_kernel<float, float>, blocks, 128, 0, stream, (const float*)x, x_stride, (const float*)w,
+                  (float*)out, out_stride, rows, width, eps);
+  else if (dtype == DT_BF16)
+    launch_kernel(rows_rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, 128, 0, stream, (const __nv_bfloat16*)x,
+                  x_stride, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, out_stride, rows, width, eps);
   else
     return ERR_BAD_DTYPE;
   return launch_status();

@@ -634,13 +634,15 @@ extern "C" int llm_attention_plain(const void* q, void* out, int dtype, void* k_
 
 // out[t, i] = act(gate[t, i]) * up[t, i] with gate = in[t, i] and up = in[t, inter + i]; `in`
 // may be a sum of partial results.  act: silu (GLU_SILU), or the tanh form of gelu,
-// 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))) (GLU_GELU_TANH).
+// 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))) (GLU_GELU_TANH), or the clamped form
+// g' = min(g, limit), u' = clamp(u, -limit, limit), out = g' sigmoid(alpha g') (u' + 1) (GLU_CLAMPED).
 #define GLU_SILU 0
 #define GLU_GELU_TANH 1
+#define GLU_CLAMPED 2
 
 template <typename TI, typename TO>
 __global__ void swiglu_kernel(const TI* __restrict__ in, int n_partials, long long partial_stride,
-                              TO* __restrict__ out, long long total, int inter, int act) {
+                              TO* __restrict__ out, long long total, int inter, int act, float limit, float alpha) {
   pdl_launch_dependents();
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -652,15 +654,20 @@ __global__ void swiglu_kernel(const TI* __restrict__ in, int n_partials, long lo
       g += to_float(in[p * partial_stride + t * 2 * inter + c]);
       u += to_float(in[p * partial_stride + t * 2 * inter + inter + c]);
     }
+    if (act == GLU_CLAMPED) {
+      g = fminf(g, limit);
+      u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+    }
     const float a = act == GLU_GELU_TANH
                         ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
-                        : g / (1.0f + expf(-g));
+                        : g / (1.0f + expf(-(act == GLU_CLAMPED ? alpha : 1.0f) * g));
     out[i] = from_float<TO>(a * u);
   }
 }
 
 static int glu_launch(const void* in, int in_dtype, int n_partials, long long partial_stride, void* out,
-                      int out_dtype, int n_tokens, int inter, int act, cudaStream_t stream);
+                      int out_dtype, int n_tokens, int inter, int act, cudaStream_t stream, float limit = 0.0f,
+                      float alpha = 1.0f);
 
 extern "C" int llm_swiglu(const void* in, int in_dtype, int n_partials, long long partial_stride,
                           void* out, int out_dtype, int n_tokens, int inter, cudaStream_t stream) {
@@ -674,14 +681,21 @@ extern "C" int llm_glu(const void* in, int in_dtype, int n_partials, long long p
   return glu_launch(in, in_dtype, n_partials, partial_stride, out, out_dtype, n_tokens, inter, act, stream);
 }
 
+// The clamped form: min(gate, limit) * sigmoid(alpha * min(gate, limit)) * (clamp(up, -limit, limit) + 1).
+extern "C" int llm_glu_clamped(const void* in, int in_dtype, int n_partials, long long partial_stride, void* out,
+                               int out_dtype, int n_tokens, int inter, float limit, float alpha, cudaStream_t stream) {
+  return glu_launch(in, in_dtype, n_partials, partial_stride, out, out_dtype, n_tokens, inter, GLU_CLAMPED, stream, limit,
+                    alpha);
+}
+
 static int glu_launch(const void* in, int in_dtype, int n_partials, long long partial_stride, void* out,
-                      int out_dtype, int n_tokens, int inter, int act, cudaStream_t stream) {
+                      int out_dtype, int n_tokens, int inter, int act, cudaStream_t stream, float limit, float alpha) {
   const long long total = (long long)n_tokens * inter;
   if (total <= 0) return 0;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
 #define LAUNCH_SWIGLU(TI, TO)                                                                    \
   launch_kernel(swiglu_kernel<TI, TO>, blocks, 256, 0, stream, (const TI*)in, n_partials,        \
-                partial_stride, (TO*)out, total, inter, act)
+                partial_stride, (TO*)out, total, inter, act, limit, alpha)
   if (in_dtype == DT_F32 && out_dtype == DT_F32) LAUNCH_SWIGLU(float, float);
   else if (in_dtype == DT_F32 && out_dtype == DT_BF16) LAUNCH_SWIGLU(float, __nv_bfloat16);
   else if (in_dtype == DT_BF16 && out_dtype == DT_BF16) LAUNCH_SWIGLU(__nv_bfloat16, __nv_bfloat16);

@@ -20,32 +20,48 @@ def lib():
     if _lib is None:
         l = build.load_library("latent_attention.cu")
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
-        l.llm_latent_prepare.argtypes = [P, I, L, I, I, I, I, I, I, P, F, P, I, F, P, P, P, L, I, I, P, P, I, I, P]
+        l.llm_latent_prepare.argtypes = [P, I, L, I, P, L, I, I, I, I, P, F, P, I, I, F, P, P, P, L, I, I, P, P, I, I, P]
+        l.llm_rows_rmsnorm.argtypes = [P, L, P, P, L, I, I, I, F, P]
         l.llm_per_head_linear.argtypes = [P, L, L, P, I, P, L, L, P, L, I, I, I, I, I, P]
         l.llm_latent_attention.argtypes = [P, P, I, P, P, L, I, I, I, I, P, P, P, I, I, F, I, P]
         l.llm_latent_attention_mma.argtypes = [P, P, P, P, P, L, I, I, I, I, P, P, P, I, I, F, I, I, P]
         l.llm_latent_attention_mma_scratch.argtypes = [I, I, I, I]
         l.llm_latent_attention_mma_scratch.restype = c_longlong
         l.llm_latent_attention_rows.argtypes = [P, P, P, P, L, I, I, I, I, P, P, P, P, P, I, I, I, F, I, P]
-        for name in ("llm_latent_prepare", "llm_per_head_linear", "llm_latent_attention", "llm_latent_attention_mma",
+        for name in ("llm_latent_prepare", "llm_rows_rmsnorm", "llm_per_head_linear", "llm_latent_attention", "llm_latent_attention_mma",
                      "llm_latent_attention_rows"):
             getattr(l, name).restype = c_int
         _lib = l
     return _lib
 
 
-def prepare(ctx, u: torch.Tensor, q_col: int, c_col: int, heads: int, dim: int, rot: int, rank: int,
-            norm_w: torch.Tensor, eps: float, inv_freq: Optional[torch.Tensor], rot_dims: int, mag: float,
-            q_full: torch.Tensor, cache: CacheView, write_cache: bool) -> None:
-    """Norms the latent, rotates the shared key part and writes both to the cache; rotates the
-    queries' rotated parts into the last `rot` entries of q_full [rows, heads, rank + rot]."""
-    _dev(u, norm_w, inv_freq, q_full)
+def prepare(ctx, u: torch.Tensor, q_col: int, c_rows: Optional[torch.Tensor], heads: int, dim: int, rot: int, rank: int,
+            norm_w: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor], rot_dims: int, mag: float,
+            q_full: torch.Tensor, cache: CacheView, write_cache: bool, halves: bool = False) -> None:
+    """Norms the latent (`c_rows` [rows, rank + rot], a column view or a matrix of its own), rotates the
+    shared key part and writes both to the cache; rotates the queries' rotated parts (u [rows, ...], the
+    queries from column `q_col`) into the last `rot` entries of q_full [rows, heads, rank + rot].  A run that
+    reads another run's cache gives no `c_rows` and writes nothing.  `halves`: entry i turns with entry
+    i + rot_dims / 2 instead of 2i with 2i + 1."""
+    _dev(u, c_rows, norm_w, inv_freq, q_full)
+    write_cache = bool(write_cache and c_rows is not None)
+    if c_rows is not None and (c_rows.dtype != u.dtype or c_rows.stride(1) != 1):
+        raise TypeError("latent prepare: the compressed rows must have the queries' element type and unit column stride")
     _check(lib().llm_latent_prepare(
-        u.data_ptr(), dtype_code(u.dtype), u.stride(0), q_col, c_col, heads, dim, rot, rank, norm_w.data_ptr(),
-        float(eps), _ptr(inv_freq), int(rot_dims), float(mag), q_full.data_ptr(), cache.k_ptr,
-        cache.block_table.data_ptr(), cache.page_stride, cache.table_stride, cache.page_tokens,
-        ctx.positions.data_ptr(), ctx.row_seq.data_ptr(), 1 if write_cache else 0, ctx.n_tokens, ctx.stream),
-        "latent_prepare")
+        u.data_ptr(), dtype_code(u.dtype), u.stride(0), q_col, _ptr(c_rows), c_rows.stride(0) if c_rows is not None else 0,
+        heads, dim, rot, rank, _ptr(norm_w), float(eps), _ptr(inv_freq), int(rot_dims), 1 if halves else 0, float(mag),
+        q_full.data_ptr(), cache.k_ptr, cache.block_table.data_ptr(), cache.page_stride, cache.table_stride,
+        cache.page_tokens, ctx.positions.data_ptr(), ctx.row_seq.data_ptr(), 1 if write_cache else 0, ctx.n_tokens,
+        ctx.stream), "latent_prepare")
+
+
+def rows_rmsnorm(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, rows: int, eps: float) -> None:
+    """out[t] = x[t] / sqrt(mean(x[t]^2) + eps) * w; x may be a column view, sums are float32."""
+    _dev(x, w, out)
+    if not (x.dtype == w.dtype == out.dtype) or x.stride(1) != 1 or out.stride(1) != 1:
+        raise TypeError("rows_rmsnorm: element types or layout not as the kernel needs")
+    _check(lib().llm_rows_rmsnorm(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0),
+                                  dtype_code(x.dtype), rows, x.shape[1], float(eps), ctx.stream), "rows_rmsnorm")
 
 
 def per_head_linear(ctx, x: torch.Tensor, w: torch.Tensor, w_in_rows: bool, out: torch.Tensor, heads: int, n_in: int,

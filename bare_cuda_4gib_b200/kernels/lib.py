@@ -99,10 +99,11 @@ class _Plain:
         lib.llm_attention_plain.argtypes = [P, P, I, P, P, P, L, I, I, I, I, P, P, I, I, F, I, P]
         lib.llm_swiglu.argtypes = [P, I, I, L, P, I, I, I, P]
         lib.llm_glu.argtypes = [P, I, I, L, P, I, I, I, I, P]
+        lib.llm_glu_clamped.argtypes = [P, I, I, L, P, I, I, I, F, F, P]
         lib.llm_argmax_rows.argtypes = [P, P, I, I, P]
         lib.llm_sample_rows.argtypes = [P, P, P, P, I, I, P]
         for name in ("llm_embed_gather", "llm_add_rmsnorm", "llm_matmul_plain", "llm_rope_cache_write",
-                     "llm_attention_plain", "llm_swiglu", "llm_glu", "llm_argmax_rows", "llm_sample_rows"):
+                     "llm_attention_plain", "llm_swiglu", "llm_glu", "llm_glu_clamped", "llm_argmax_rows", "llm_sample_rows"):
             getattr(lib, name).restype = c_int
         self.lib = lib
 
@@ -275,6 +276,16 @@ def glu(gate_up: Partials, out: torch.Tensor, n_tokens: int, activation: str, st
     _check(plain().lib.llm_glu(gate_up.tensor.data_ptr(), dtype_code(gate_up.tensor.dtype), gate_up.n, gate_up.stride,
                                out.data_ptr(), dtype_code(out.dtype), n_tokens, out.shape[-1],
                                GLU_ACTIVATIONS[activation], stream if stream is not None else stream_handle()), "glu")
+
+
+def glu_clamped(gate_up: Partials, out: torch.Tensor, n_tokens: int, limit: float, alpha: float, stream=None) -> None:
+    """out = g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), of
+    [gate | up] (possibly a sum of partial results)."""
+    _dev(gate_up.tensor, out)
+    _check(plain().lib.llm_glu_clamped(gate_up.tensor.data_ptr(), dtype_code(gate_up.tensor.dtype), gate_up.n,
+                                       gate_up.stride, out.data_ptr(), dtype_code(out.dtype), n_tokens, out.shape[-1],
+                                       float(limit), float(alpha), stream if stream is not None else stream_handle()),
+           "glu_clamped")
 
 
 def argmax_rows(logits: torch.Tensor, out: torch.Tensor, rows: int, stream=None) -> None:

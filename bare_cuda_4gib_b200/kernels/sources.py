@@ -7,7 +7,7 @@ ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128)
 def all_libraries():
     jobs = [("plain_kernels.cu", ()), ("gemm_tcgen05.cu", ()), ("gemv_fused.cu", ()), ("stream_kernels.cu", ()),
             ("linear_attention.cu", ()), ("biased_attention.cu", ()), ("sandwich_norm.cu", ()), ("head_prepare.cu", ()),
-            ("latent_attention.cu", ()), ("mlstm.cu", ())]
+            ("latent_attention.cu", ()), ("mlstm.cu", ()), ("diff_attention.cu", ()), ("moe.cu", ())]
     jobs += [("gemm_tcgen05.cu", ("-DGLU_GELU_TANH",)), ("gemv_fused.cu", ("-DGLU_GELU_TANH",))]
     jobs += [("attention_mma.cu", (f"-DHEAD_DIM={d}",)) for d in ATTENTION_HEAD_DIMS]
     jobs += [("attention_mma.cu", (f"-DHEAD_DIM={d}", "-DDISTANCE_BIAS")) for d in ATTENTION_HEAD_DIMS]

@@ -1,7 +1,7 @@
 """Arrangement of a mixer and a feed-forward in one layer.
 
-"prenorm": x += mixer(norm(x)); x += feed_forward(norm(x))
-(cuongvng/bare-cuda-4gib engine/src/model.cpp:526-604).  Each add is carried out by the norm
+"prenorm": x += mixer(norm(x)); x += feed_forward(norm(x)), the second only where the layer has a
+feed-forward (cuongvng/bare-cuda-4gib engine/src/model.cpp:526-604).  Each add is carried out by the norm
 that follows it, so a layer hands its last contribution on, not yet added, as `pending` - unless
 the part's last kernel added it into the residual stream itself (`ctx.residual`), in which case the
 part returns None.
@@ -17,11 +17,12 @@ class PreNormBlock:
     def __init__(self, layer_spec):
         self.mixer_norm = build_part("norm", layer_spec.mixer_norm)
         self.mixer = build_part("mixer", layer_spec.mixer)
-        self.ffn_norm = build_part("norm", layer_spec.ffn_norm)
-        self.ffn = build_part("feed_forward", layer_spec.ffn)
+        self.has_ffn = layer_spec.ffn is not None
+        self.ffn_norm = build_part("norm", layer_spec.ffn_norm) if self.has_ffn else None
+        self.ffn = build_part("feed_forward", layer_spec.ffn) if self.has_ffn else None
 
     def parts(self):
-        return [self.mixer_norm, self.mixer, self.ffn_norm, self.ffn]
+        return [self.mixer_norm, self.mixer] + ([self.ffn_norm, self.ffn] if self.has_ffn else [])
 
     def cache_demands(self):
         """What this layer keeps per request: its mixer's paged cache and state."""
@@ -32,8 +33,11 @@ class PreNormBlock:
         ctx.residual = residual      # a part may add its contribution here itself and return None
         after = getattr(ctx, "norm_after_layer", None)
         h = self.mixer_norm.forward(ctx, residual, pending, n, lazy=getattr(self.mixer, "takes_lazy_input", False))
-        ctx.following_norm = self.ffn_norm     # the norm that reads the stream after the part that runs now
+        ctx.following_norm = self.ffn_norm if self.has_ffn else after     # the norm that reads the stream next
         mixed = self.mixer.forward(ctx, call, h)
+        if not self.has_ffn:
+            ctx.following_norm = None
+            return mixed
         h = self.ffn_norm.forward(ctx, residual, mixed, n, lazy=getattr(self.ffn, "takes_lazy_input", False))
         ctx.following_norm = after
         out = self.ffn.forward(ctx, h)

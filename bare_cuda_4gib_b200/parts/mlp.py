@@ -79,9 +79,11 @@ class DenseFeedForward(Part):
 class GatedFeedForward(Part):
     """down(act(gate(h)) * up(h)), no biases; `activation` is "silu" or "gelu_tanh" (the tanh form of
     gelu).  gate and up are one matrix product against [Wgate; Wup]; the kernels that fuse the
-    activation into that product do so for both activations.
+    activation into that product do so for both activations.  A third form, "clamped_swish", bounds
+    both factors first: g = min(gate(h), limit), u = clamp(up(h), -limit, limit), and the product is
+    g sigmoid(alpha g) (u + 1); it runs as a kernel of its own behind the [gate; up] product.
 
-    params: `hidden`, `intermediate`, `activation`.  tensors: `gate`, `up`, `down`."""
+    params: `hidden`, `intermediate`, `activation` (, `limit`, `alpha`).  tensors: `gate`, `up`, `down`."""
 
     takes_lazy_input = False
 
@@ -94,8 +96,12 @@ class GatedFeedForward(Part):
 
     def prepare(self, dtype, device) -> None:
         self.activation = self.params.get("activation", "silu")
-        if self.activation not in K.GLU_ACTIVATIONS:
-            raise KeyError(f"glu feed-forward: activation '{self.activation}' is not one of {sorted(K.GLU_ACTIVATIONS)}")
+        self.clamped = self.activation == "clamped_swish"
+        if self.clamped:
+            self.limit, self.alpha = float(self.params["limit"]), float(self.params.get("alpha", 1.0))
+        elif self.activation not in K.GLU_ACTIVATIONS:
+            raise KeyError(f"glu feed-forward: activation '{self.activation}' is not one of "
+                           f"{sorted(K.GLU_ACTIVATIONS) + ['clamped_swish']}")
         t = self.tensors
         self.gate_up = Linear(fused_rows([t.pop("gate"), t.pop("up")]), "gate_up")
         self.down = Linear(t.pop("down"), "down")
@@ -104,5 +110,10 @@ class GatedFeedForward(Part):
 
     def forward(self, ctx, h):
         n = ctx.n_tokens
+        if self.clamped:
+            both = self.gate_up.forward(ctx, h, n, torch.float32 if n <= 256 else ctx.dtype, "ffn_gate_up", allow_partials=True)
+            act = ctx.ws.get("ffn_act", (n, int(self.params["intermediate"])), ctx.dtype)
+            K.glu_clamped(both, act, n, self.limit, self.alpha, ctx.stream)
+            return self.down.forward(ctx, act, n, torch.float32, "ffn_out", allow_partials=True)
         act = self.gate_up.forward(ctx, h, n, ctx.dtype, "ffn_act", glu=self.activation)
         return self.down.forward(ctx, act.tensor, n, torch.float32, "ffn_out", allow_partials=True)

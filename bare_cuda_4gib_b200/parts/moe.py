@@ -1,0 +1,110 @@
+"""A mixture-of-experts feed-forward.
+
+    z = W_router h (float32);  s = softmax(z) over all experts;  the `top` experts with the largest s are
+    chosen (the lowest index wins a tie);  weight_e = s_e * router_scale, not renormalised;
+    out = sum over the chosen e of weight_e * W_down,e (silu(W_gate,e h) * (W_up,e h));
+    with a shared expert (same form, its own size):  out += sigmoid(w_sg . h) * shared(h), one gate per token.
+
+The experts' matrices are stacked ([experts, 2 * ff, hidden] with an expert's gate rows before its up
+rows, and [experts, hidden, ff]); a step's (token, choice) slots are grouped by expert on the device, and
+two grouped products walk the groups, so no host decision depends on the router and a step is captured
+in a CUDA graph like any other.  A row's sums run over the inner index in order, and a token's slots are
+added in the order of the choice, so a token's result does not depend on what else is in the step.  The
+shared expert runs on the engine's dense products.
+
+params: `hidden`, `experts`, `top`, `router_scale`, `intermediate`, `shared_intermediate` (None: no shared
+expert), `shared_gate` (bool).  tensors: `router` [experts, hidden], `e<j>.gate|up` [intermediate, hidden],
+`e<j>.down` [hidden, intermediate], `shared.gate|up|down`, `shared.sg` [1, hidden].
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..errors import ConfigError
+from ..kernels import lib as K
+from .base import Part
+from .linear import Linear
+from .registry import register_feed_forward
+from ..weights.loader import fused_rows
+
+
+@register_feed_forward("moe")
+class MixtureOfExperts(Part):
+    takes_lazy_input = False
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden, self.experts, self.top, self.ff = int(p["hidden"]), int(p["experts"]), int(p["top"]), int(p["intermediate"])
+        self.router_scale = float(p.get("router_scale", 1.0))
+        self.shared_ff = int(p["shared_intermediate"]) if p.get("shared_intermediate") else 0
+        self.has_shared_gate = bool(p.get("shared_gate")) and self.shared_ff > 0
+        from ..kernels.moe import MAX_EXPERTS
+        if not (1 <= self.top <= self.experts <= MAX_EXPERTS):
+            raise ConfigError(f"moe: {self.top} of {self.experts} experts (at most {MAX_EXPERTS}) cannot be chosen")
+
+    def local_weights(self):
+        out = {"router": ((self.experts, self.hidden), "matrix")}
+        for e in range(self.experts):
+            out[f"e{e}.gate"] = ((self.ff, self.hidden), "matrix")
+            out[f"e{e}.up"] = ((self.ff, self.hidden), "matrix")
+            out[f"e{e}.down"] = ((self.hidden, self.ff), "matrix")
+        if self.shared_ff:
+            out["shared.gate"] = ((self.shared_ff, self.hidden), "matrix")
+            out["shared.up"] = ((self.shared_ff, self.hidden), "matrix")
+            out["shared.down"] = ((self.hidden, self.shared_ff), "matrix")
+            if self.has_shared_gate:
+                out["shared.sg"] = ((1, self.hidden), "matrix")
+        return out
+
+    def adjacent_weights(self):
+        groups = [tuple(f"e{e}.{t}" for e in range(self.experts) for t in ("gate", "up")),
+                  tuple(f"e{e}.down" for e in range(self.experts))]
+        if self.shared_ff:
+            groups.append(("shared.gate", "shared.up"))
+        return groups
+
+    def prepare(self, dtype, device) -> None:
+        t = self.tensors
+        E = self.experts
+        self.w_up = fused_rows([t[f"e{e}.{n}"] for e in range(E) for n in ("gate", "up")]).to(dtype).contiguous()
+        self.w_down = fused_rows([t[f"e{e}.down"] for e in range(E)]).to(dtype).contiguous()
+        self.w_router = t["router"].contiguous()
+        self.w_sg = t["shared.sg"].to(self.w_router.dtype).reshape(-1).contiguous() if self.has_shared_gate else None
+        if self.shared_ff:
+            self.shared_gate_up = Linear(fused_rows([t["shared.gate"], t["shared.up"]]), "moe.shared.gate_up")
+            self.shared_down = Linear(t["shared.down"], "moe.shared.down")
+            self.shared_gate_up.prepare(dtype)
+            self.shared_down.prepare(dtype)
+        for e in range(E):      # the stacked matrices stand for them from here on
+            for n in ("gate", "up", "down"):
+                t.pop(f"e{e}.{n}")
+        t["experts.up"], t["experts.down"] = self.w_up, self.w_down
+
+    def forward(self, ctx, h):
+        from ..kernels import moe as M
+        n, top, E = ctx.n_tokens, self.top, self.experts
+        slots = n * top
+        i32, f32 = torch.int32, torch.float32
+        ids = ctx.ws.get("moe_ids", (n, top), i32)
+        weights = ctx.ws.get("moe_weights", (n, top), f32)
+        gate = ctx.ws.get("moe_shared_gate", (n, 1), f32) if self.has_shared_gate else None
+        sorted_slots = ctx.ws.get("moe_sorted", (n, top), i32)
+        # room for every tile a step of this shape can make, three numbers each, and their count
+        tiles = ctx.ws.get("moe_tiles", (n, 3 * (top + E) + 1), i32)
+        n_tiles = tiles.view(-1)[3 * M.max_tiles(slots, E):]
+        M.route(ctx, h, self.w_router, self.w_sg, top, self.router_scale, ids, weights, gate, n)
+        M.sort(ctx, ids, slots, E, sorted_slots, tiles, n_tiles)
+        act = ctx.ws.get("moe_act", (n, top * self.ff), ctx.dtype)
+        M.grouped(ctx, h, self.w_up, act, False, sorted_slots, tiles, n_tiles, weights, top, self.ff, self.hidden, slots, E)
+        y = ctx.ws.get("moe_y", (n, top * self.hidden), f32)
+        M.grouped(ctx, act.view(-1)[: slots * self.ff].view(slots, self.ff), self.w_down, y, True, sorted_slots, tiles,
+                  n_tiles, weights, top, self.hidden, self.ff, slots, E)
+        shared = None
+        if self.shared_ff:
+            a = self.shared_gate_up.forward(ctx, h, n, ctx.dtype, "moe_shared_act", glu="silu")
+            shared = self.shared_down.forward(ctx, a.tensor, n, f32, "moe_shared_out", allow_partials=True)
+        out = ctx.ws.get("ffn_out", (n, self.hidden), f32)
+        M.combine(ctx, y, top, shared, gate, out, n, self.hidden)
+        return K.Partials(out)

@@ -5,7 +5,8 @@ multiplied last (cuongvng/bare-cuda-4gib engine/kernels/rmsnorm.cu:26-40).  The 
 the residual in a kernel of its own (engine/kernels/residual_add.cu:20); here the add of the
 previous part's contribution and the norm are one kernel, and the residual stream stays float32.
 
-params: `size` (width), `eps`.  tensors: `weight` [size].
+params: `size` (width), `eps`, `one_plus` (optional: the weight is stored around zero and the factor
+is 1 + w, formed once in float32).  tensors: `weight` [size].
 """
 
 from __future__ import annotations
@@ -23,8 +24,19 @@ from .registry import register_norm
 class RMSNorm(Part):
     prenormable = True      # the norm's factor is one number per row (see kernels.lib.AddTo)
 
+    def __init__(self, spec):
+        super().__init__(spec)
+        if self.params.get("one_plus"):
+            # 1 + w needs more digits than a 16-bit weight has: it stays float32, and the products that
+            # norm their own input (which take the weight in the step's type) are not offered this norm
+            self.prenormable = False
+
     def local_weights(self):
-        return {"weight": ((self.params["size"],), "norm")}
+        return {"weight": ((self.params["size"],), "zero" if self.params.get("one_plus") else "norm")}
+
+    def prepare(self, dtype, device) -> None:
+        if self.params.get("one_plus"):
+            self.tensors["weight"] = (1.0 + self.tensors["weight"].to(torch.float32)).contiguous()
 
     def forward(self, ctx, residual: torch.Tensor, delta: Optional[K.Partials], rows: int,
                 row_index: Optional[torch.Tensor] = None, buffer: str = "normed", lazy: bool = False):
@@ -32,7 +44,7 @@ class RMSNorm(Part):
         step gets the norm as a description that the consuming product computes in its own kernel."""
         left = getattr(ctx, "prenormed", None)       # what the last adding product may have left for this norm
         ctx.prenormed = None
-        if lazy and delta is None and ctx.dtype == torch.bfloat16 and ctx.use_fast_gemm:
+        if lazy and delta is None and ctx.dtype == torch.bfloat16 and ctx.use_fast_gemm and self.prenormable:
             from ..kernels import gemv
             mine = left if left is not None and left.norm is self else None
             # a few-token step norms inside the consuming product; a many-token step only where the

@@ -76,3 +76,25 @@ class PairwiseRotaryPositions(Part):
 
     def fused_rotation(self):
         return None      # the pairing differs from the one the fused attention kernels apply
+
+
+@register_position("rotary_halves")
+class HalvesRotaryPositions(Part):
+    """Rotation of the first `dims` entries of a head (or of a map of a head) with entry i paired with
+    entry i + dims / 2 (the rest pass) by the angle position * f_i, f_i = base^(-2i / dims): the pair
+    (u, v) becomes (u cos - v sin, v cos + u sin).
+
+    The kernels that norm and cache q and k turn them with `inv_freq` themselves (`halves` tells them
+    the pairing).  params: `dims`, `base`.  No tensors."""
+
+    halves = True
+    magnitude = 1.0
+
+    def prepare(self, dtype, device) -> None:
+        dims, base = int(self.params["dims"]), float(self.params["base"])
+        self.dims = dims
+        i = torch.arange(dims // 2, dtype=torch.float64)
+        self.inv_freq = (base ** (-2.0 * i / dims)).to(torch.float32).to(device)
+
+    def fused_rotation(self):
+        return None      # the fused attention kernels turn whole heads; this one may turn a head's first entries only

@@ -53,7 +53,7 @@ class WeightSpec:
     name: str                 # name in the file
     shape: Tuple[int, ...]    # an extent of -1 is taken from the file (random weights need every extent)
     init: str = "matrix"      # random-weights mode: "matrix" ~ N(0, 0.02); "norm" ~ 1 + N(0, 0.01);
-                              # "identity" ~ I + N(0, 0.01); "unit" ~ N(0, 1)
+                              # "identity" ~ I + N(0, 0.01); "unit" ~ N(0, 1); "zero" ~ N(0, 0.01)
     integer: bool = False     # integer tables are kept as int32
 
 

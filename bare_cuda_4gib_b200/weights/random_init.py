@@ -1,7 +1,7 @@
 """Random-weights mode: writes a model folder (config.json, model.safetensors) from a
 configuration and a seed.
 
-Matrices and tables ~ N(0, 0.02), norm weights ~ 1 + N(0, 0.01).  Every tensor has a generator
+Matrices and tables ~ N(0, 0.02), norm weights ~ 1 + N(0, 0.01) (stored around zero: N(0, 0.01)).  Every tensor has a generator
 of its own, seeded from the seed and the tensor's name, so a tensor's values do not depend on
 which other tensors exist.  (cuongvng/bare-cuda-4gib has random weights only in its torch
 fixture: tools/references/reference_forward.py:301-321.)
@@ -39,6 +39,8 @@ def random_tensor(spec: WeightSpec, seed: int, name: str, dtype: torch.dtype, de
     x = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
     if spec.init == "norm":
         x = 1.0 + NORM_STD * x
+    elif spec.init == "zero":
+        x = NORM_STD * x
     elif spec.init == "identity":
         x = torch.eye(spec.shape[0], spec.shape[1], dtype=torch.float32, device=device) + NORM_STD * x
     elif spec.init != "unit":
