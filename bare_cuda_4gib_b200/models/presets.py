@@ -76,6 +76,35 @@ PRESETS.update({
 })
 
 
+def _pudulorn(width, vocab, ff, heads, kv_heads, dim, vdim, chunk, latent_heads, latent_dim, rot_dim, kv_rank, q_rank,
+              window, experts, top, expert_ff, blocks):
+    """`blocks` times: differential attention with a dense feed-forward, latent attention with a mixture of experts,
+    differential attention again, and a latent layer that reads the cached latent of the block's first one."""
+    attention = {"type": "attention", "mlp": {"kind": "dense", "ff": ff, "limit": 7.0},
+                 "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "diff": 0.8,
+                           "mask": {"size": chunk}, "rot": {"base": 10000.0, "dims": dim}, "scale": dim ** -0.5}}
+    latent = {"type": "latent_attention",
+              "mlp": {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "scale": 1.0},
+                      "shared": {"ff": expert_ff}},
+              "mixer": {"heads": latent_heads, "dim": latent_dim, "rot_dim": rot_dim, "vdim": latent_dim, "kv_rank": kv_rank,
+                        "q_rank": q_rank, "mask": {"size": window}, "rot": {"base": 10000.0, "dims": rot_dim},
+                        "scale": (latent_dim + rot_dim) ** -0.5}}
+    layers = []
+    for b in range(blocks):
+        layers += [attention, latent, attention, dict(latent, mixer=dict(latent["mixer"], kv_from=4 * b + 1))]
+    return dict(architecture="Pudulorn", vocab=vocab, width=width, norm={"eps": 1e-6}, layers=layers)
+
+
+PRESETS.update({
+    "pudulorn-tiny": _pudulorn(64, 300, 96, 4, 2, 16, 24, 24, 2, 16, 8, 24, 32, 20, 4, 2, 32, 1),
+    # layer sizes near TinyLlama's (width 2048, feed-forward 5632): 16 heads of two maps of 64, values of 128;
+    # eight experts of which two (plus the shared one) give a token 3 x 1,408 feed-forward rows of the dense 5,632 x 3/4
+    "pudulorn-2048": _pudulorn(2048, 32000, 5632, 16, 4, 64, 128, 1024, 16, 64, 32, 256, 768, 1024, 8, 2, 1408, 2),
+    # ... and near Llama-2-7B's (width 4096, feed-forward 11008)
+    "pudulorn-4096": _pudulorn(4096, 32000, 11008, 16, 8, 128, 256, 1024, 32, 128, 64, 512, 1536, 1024, 8, 2, 2752, 2),
+})
+
+
 def preset_config(name: str, **overrides):
     from ..config.llama import LlamaConfig
     from ..errors import ConfigError

@@ -186,7 +186,7 @@ SETTLE_SECONDS = 0.1      # pause between putting the prompts into the cache and
 
 
 def design_main(args) -> int:
-    """`--design dopudra` or `--design zadurax`: one JSON line with, per size, a prefill step of `--prefill-tokens` tokens and decode
+    """`--design dopudra`, `zadurax` or `pudulorn`: one JSON line with, per size, a prefill step of `--prefill-tokens` tokens and decode
     steps at `--batch` requests of `--context` positions for the design and for the Llama decoder of the same
     width, both with `--design-layers` layers, seeded random weights, bfloat16, CUDA events around the steps."""
     import torch
@@ -288,7 +288,7 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode"],
                     help="profiling aid: run just the prefill step or just the decode steps and print their time")
-    ap.add_argument("--design", default="", choices=["", "dopudra", "zadurax"],
+    ap.add_argument("--design", default="", choices=["", "dopudra", "zadurax", "pudulorn"],
                     help="instead of the default workload: prefill and decode throughput of this design at layer sizes "
                          "of real models, beside the Llama decoder at equal width, layer count and vocabulary")
     ap.add_argument("--design-layers", type=int, default=8, help="layers of both models in a --design run")
