@@ -126,17 +126,23 @@ def expert(t, p, h):
     return (z * torch.sigmoid(z) * (h @ t[p + "up"].T)) @ t[p + "down"].T
 
 
-def router(t, p, mlp, h):
-    """[n, experts]: score times router scale for a token's chosen experts, zero for the others."""
+def router(t, p, mlp, h, margins=None):
+    """[n, experts]: score times router scale for a token's chosen experts, zero for the others.
+    `margins` (a list) receives, per token, how far the last chosen score lies above the first one
+    left out, relative to itself (1 where every expert is chosen)."""
     r = mlp["router"]
     s = torch.softmax(h @ t[p + "router"].T, -1)
     chosen = torch.topk(s, r["top"], -1).indices
     keep = torch.zeros_like(s).scatter_(1, chosen, 1.0)
+    if margins is not None:
+        v = torch.sort(s, -1, descending=True).values
+        top = r["top"]
+        margins.append((v[:, top - 1] - v[:, top]) / v[:, top - 1] if top < s.shape[1] else torch.ones_like(v[:, 0]))
     return s * keep * r["scale"]
 
 
-def mixture_of_experts(t, p, mlp, h):
-    w = router(t, p, mlp, h)
+def mixture_of_experts(t, p, mlp, h, margins=None):
+    w = router(t, p, mlp, h, margins)
     out = torch.zeros_like(h)
     for e in range(mlp["router"]["experts"]):
         rows = torch.nonzero(w[:, e] != 0).flatten()
@@ -147,12 +153,14 @@ def mixture_of_experts(t, p, mlp, h):
     return out
 
 
-def feed_forward(t, p, mlp, h):
-    return clamped_feed_forward(t, p, mlp, h) if mlp["kind"] == "dense" else mixture_of_experts(t, p, mlp, h)
+def feed_forward(t, p, mlp, h, margins=None):
+    return clamped_feed_forward(t, p, mlp, h) if mlp["kind"] == "dense" else mixture_of_experts(t, p, mlp, h, margins)
 
 
-def forward(cfg, tensors: Dict[str, torch.Tensor], ids: List[int], streams: Optional[list] = None) -> torch.Tensor:
-    """Logits [n, vocab] of one sequence; with `streams` a list, the residual stream after every layer is appended."""
+def forward(cfg, tensors: Dict[str, torch.Tensor], ids: List[int], streams: Optional[list] = None,
+            margins: Optional[list] = None) -> torch.Tensor:
+    """Logits [n, vocab] of one sequence; with `streams` a list, the residual stream after every layer is appended;
+    with `margins` a list, every router's per-token margin between the chosen and the other experts."""
     t = {k: v.to(F64) for k, v in tensors.items()}
     eps = cfg["norm"]["eps"]
     x = t["embed"][torch.tensor(ids)]
@@ -167,7 +175,7 @@ def forward(cfg, tensors: Dict[str, torch.Tensor], ids: List[int], streams: Opti
             y, cached[i] = latent_attention(t, p + "mix.", m, h, eps, None if src is None else cached[src])
             x = x + y
         if layer.get("mlp") is not None:
-            x = x + feed_forward(t, p + "mlp.", layer["mlp"], rms_norm_around_zero(x, t[p + "norm2"], eps))
+            x = x + feed_forward(t, p + "mlp.", layer["mlp"], rms_norm_around_zero(x, t[p + "norm2"], eps), margins)
         if streams is not None:
             streams.append(x.clone())
     return rms_norm_around_zero(x, t["final.norm"], eps) @ t["head"].T

@@ -165,6 +165,24 @@ def plain_logits(folder, ids: Sequence[int]) -> torch.Tensor:
     return _plain[key]
 
 
+CLEAR_MARGIN = 1e-3
+
+
+def clear_ids(folder, rng, n: int, vocab: int) -> List[int]:
+    """`n` random ids on which no router of the model in `folder` makes a close call: where the last chosen
+    expert's score lies within `CLEAR_MARGIN` (relative) of the first one left out, float32 rounding may
+    choose the other, which is no fault; such a draw is thrown away and the next one taken."""
+    cfg = json.loads((folder / "config.json").read_text())
+    for _ in range(50):
+        ids = H.random_ids(rng, n, vocab)
+        margins: list = []
+        logits = P.forward(cfg, _tensors[str(folder)], ids, None, margins)
+        if all(float(m.min()) > CLEAR_MARGIN for m in margins):
+            _plain[(str(folder), tuple(ids))] = logits
+            return ids
+    raise AssertionError("no draw without a close call of a router")
+
+
 def check(folder, requests: Dict[str, List[int]], got, dtype: str, expect_all: bool = True) -> None:
     errors = []
     for rid, ids in requests.items():
