@@ -2,6 +2,8 @@
 needs at first use; `all_libraries()` is everything, for the build check."""
 
 ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 80, 96, 112, 128)
+# (entries of one map, value entries) of differential attention on the tensor cores, as the presets have them
+DIFF_ATTENTION_SIZES = ((16, 16), (64, 128), (128, 256))
 
 
 def all_libraries():
@@ -13,4 +15,5 @@ def all_libraries():
     jobs += [("attention_mma.cu", (f"-DHEAD_DIM={d}", "-DDISTANCE_BIAS")) for d in ATTENTION_HEAD_DIMS]
     jobs += [("attention_tcgen05.cu", (f"-DHEAD_DIM={d}",)) for d in (64, 128)]
     jobs += [("attention_decode.cu", (f"-DHEAD_DIM={d}",)) for d in (64, 128)]
+    jobs += [("diff_attention.cu", (f"-DDA_DQ={d}", f"-DDA_DV={v}")) for d, v in DIFF_ATTENTION_SIZES]
     return jobs
