@@ -164,6 +164,15 @@ struct RowsExtra {
   int pre_w_dtype;
   float* pre_sq;
   long long pre_sq_stride;
+  // Grouped products (a mixture of experts): `group_tiles` lists (group, first row, rows) per token
+  // tile, `*group_n_tiles` of them; a tile's 128 rows start at its first row (of which `rows` count) and
+  // its weight rows at group * group_w_rows.  Null: one weight matrix for all rows.
+  const int32_t* group_tiles;
+  const int32_t* group_n_tiles;
+  int group_w_rows;
+  // Row t of the product is stored at row row_map[t] of `out`, times row_weight[row_map[t]].  Null: neither.
+  const int32_t* row_map;
+  const float* row_weight;
 };
 
 constexpr int STAGING_BYTES = 4 * 32 * 32 * 4;   // per epilogue warp 32 rows of 32 float32, for the adding epilogue
@@ -286,7 +295,12 @@ __device__ __forceinline__ void epilogue_tokens_on_rows(uint32_t lane_base, int 
     return;
   }
   const int t = t_first + lane;
-  const float rs = row_scale(ex, t, n_tokens);
+  float rs = row_scale(ex, t, n_tokens);
+  int t_out = t;
+  if (ex.row_map && t < n_tokens) {
+    t_out = ex.row_map[t];
+    if (ex.row_weight) rs *= ex.row_weight[t_out];
+  }
   if (!wait_acc()) return;
   const bool vec_ok = out_is_f32 ? (ld_out % 4 == 0 && (reinterpret_cast<uintptr_t>(out_f32) & 15) == 0)
                                  : (ld_out % 8 == 0 && (reinterpret_cast<uintptr_t>(out_bf16) & 15) == 0);
@@ -312,7 +326,7 @@ __device__ __forceinline__ void epilogue_tokens_on_rows(uint32_t lane_base, int 
       if (MODE == 1) v[j] = glu_act(v[j]) * (__uint_as_float(u[j]) * rs);
     }
     const int f = f0 + c0;
-    const long long at = (long long)t * ld_out + f;
+    const long long at = (long long)t_out * ld_out + f;
     if (vec_ok && f + 16 <= n_features) {
       if (out_is_f32) {
         float4* dst = reinterpret_cast<float4*>(out_f32 + at);
@@ -422,7 +436,16 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
   // (MODE 1: BN/2 outputs).
   const int F_TILE = ORIENT == 0 ? (MODE == 1 ? BM / 2 : BM) : (MODE == 1 ? BN / 2 : BN);
   const int f0 = blockIdx.x * F_TILE;
-  const int t0 = blockIdx.y * (ORIENT == 0 ? BN : BM);
+  int t0 = blockIdx.y * (ORIENT == 0 ? BN : BM);
+  int w_row0 = 0;   // a grouped product: the first weight row of this tile's group
+  if (ORIENT == 1 && ex.group_tiles) {
+    pdl_wait();     // the list of tiles is another kernel's result
+    if ((int)blockIdx.y >= *ex.group_n_tiles) return;   // (the whole block, before it holds anything)
+    const int32_t* tile = ex.group_tiles + 3 * blockIdx.y;
+    w_row0 = tile[0] * ex.group_w_rows;
+    t0 = tile[1];
+    n_tokens = t0 + tile[2];   // rows behind the tile's own are another group's: computed, never stored
+  }
   const int kb_begin = blockIdx.z * k_blocks_per_split;
   const int kb_end = min(k_blocks, kb_begin + k_blocks_per_split);
   const int n_kb = max(0, kb_end - kb_begin);
@@ -440,9 +463,10 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
       if (MODE == 1 && which != 0) tma_load_2d(stage + A_BYTES / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
     } else {
       uint8_t* b_tile = stage + A_BYTES;
-      if (which != 1) tma_load_2d(b_tile, &map_w, &full_bar[s], k0, f0);
+      if (which != 1) tma_load_2d(b_tile, &map_w, &full_bar[s], k0, w_row0 + f0);
       // MODE 1: map_w's box has BN/2 rows: gate rows above, the matching up rows below
-      if (MODE == 1 && which != 0) tma_load_2d(b_tile + geo.b_bytes / 2, &map_w, &full_bar[s], k0, up_row_offset + f0);
+      if (MODE == 1 && which != 0)
+        tma_load_2d(b_tile + geo.b_bytes / 2, &map_w, &full_bar[s], k0, w_row0 + up_row_offset + f0);
     }
   };
   auto issue_activations = [&](int i, int s) {
@@ -912,6 +936,45 @@ extern "C" int llm_gemm_tensor_map(void* map_out, const void* base, long long ro
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : 2000 + (int)r;
+}
+
+// A grouped product for a mixture of experts (tokens on the MMA rows): `tiles` lists (group, first
+// row, rows) for `*n_tiles` <= max_tiles tiles of at most 128 rows of `map_a`'s matrix, whose rows are
+// grouped; a tile's weights are rows group * group_w_rows .. of `map_w`'s matrix (all groups stacked).
+// mode 1: a group's rows are [gate; up] with the up rows `up_row_offset` behind, and n_features counts the
+// outputs silu(gate) * up.  `row_map` (or null): row t goes to row row_map[t] of out, times
+// row_weight[row_map[t]] (or null).  map_a's box has 128 rows, map_w's bn (bn / 2 in mode 1).
+extern "C" int llm_gemm_grouped_bf16(const void* map_w, const void* map_a, void* out, int out_dtype, int max_tiles,
+                                     int n_features, int K, long long ld_out, int bn, int mode, int up_row_offset,
+                                     int group_w_rows, const int32_t* tiles, const int32_t* n_tiles,
+                                     const int32_t* row_map, const float* row_weight, int* error_word,
+                                     cudaStream_t stream) {
+  if (max_tiles <= 0 || n_features <= 0) return 0;
+  if (K <= 0 || !tiles || !n_tiles || group_w_rows <= 0) return ERR_BAD_SIZE;
+  if (out_dtype != DT_F32 && out_dtype != DT_BF16) return ERR_BAD_DTYPE;
+  if (bn < 16 || bn > 256 || bn % 16 || (mode == 1 && bn % 32) || (mode != 0 && mode != 1)) return ERR_BAD_SIZE;
+  CUtensorMap mw, ma;
+  memcpy(&mw, map_w, sizeof(CUtensorMap));
+  memcpy(&ma, map_a, sizeof(CUtensorMap));
+  RowsExtra ex = {};
+  ex.group_tiles = tiles, ex.group_n_tiles = n_tiles, ex.group_w_rows = group_w_rows;
+  ex.row_map = row_map, ex.row_weight = row_weight;
+  const int f32 = out_dtype == DT_F32 ? 1 : 0;
+  const Geometry two = make_geometry(bn, mode, 1, 2);
+  const long long f_tile = mode == 1 ? bn / 2 : bn;
+  const long long blocks = ((n_features + f_tile - 1) / f_tile) * max_tiles;
+  const bool pair = blocks > sm_count() && two.tmem_cols <= 256 && two.stages >= (mode == 1 ? 2 : 3);
+  const int rows_bound = max_tiles * BM;   // sizes the grid only: every tile brings its own rows
+#define GROUPED_CASE(MODE_)                                                                                           \
+  if (mode == MODE_)                                                                                                  \
+    return pair ? launch<MODE_, 1, 2>(bn, &mw, &ma, out, f32, rows_bound, n_features, K, ld_out, 0, 1, up_row_offset, \
+                                      ex, error_word, stream)                                                         \
+                : launch<MODE_, 1, 1>(bn, &mw, &ma, out, f32, rows_bound, n_features, K, ld_out, 0, 1, up_row_offset, \
+                                      ex, error_word, stream)
+  GROUPED_CASE(0);
+  GROUPED_CASE(1);
+  return ERR_BAD_SIZE;
+#undef GROUPED_CASE
 }
 
 // For tests of the bounded waits: the launches that follow give up on an mbarrier after `wait_ns`

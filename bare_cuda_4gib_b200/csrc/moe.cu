@@ -7,11 +7,12 @@
 // plus, where the layer has one, a shared expert that every token uses, times sigmoid(w_sg . h).
 // Router logits, softmax, weights and the shared gate are float32.
 //
-// Kernels: moe_route (a warp per token: logits, softmax, choice, weights, shared gate), moe_sort (one
+// Kernels: moe_route (a block per token: logits, softmax, choice, weights, shared gate), moe_sort (one
 // block: tokens' slots grouped by expert, and the list of row tiles the grouped products walk),
-// moe_grouped (the experts' products over those tiles: rows gathered by the list, one expert's matrix
-// per tile; float32 sums in the order of the inner index, so a row's result does not depend on what
-// else is in the step), moe_combine (adds a token's slots in the order of k, and the shared expert).
+// moe_grouped (the experts' products over those tiles in plain arithmetic, any element type: rows gathered
+// by the list, one expert's matrix per tile; float32 sums in the order of the inner index, so a row's
+// result does not depend on what else is in the step; bfloat16 steps run the tensor-core product of
+// gemm_tcgen05.cu over the same list instead, on rows that moe_gather_rows put in the list's order), moe_combine (adds a token's slots in the order of k, and the shared expert).
 
 #include "common.cuh"
 
@@ -27,26 +28,25 @@ moe_route_kernel(const T* __restrict__ h, long long h_stride, const TW* __restri
                  int32_t* __restrict__ ids, float* __restrict__ weights, float* __restrict__ shared_gate, int n_tokens) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float score[MOE_ROUTE_WARPS][MOE_MAX_EXPERTS];
+  // a block per token: its warps share the experts' dot products (and the shared gate's, counted as one
+  // more), each a warp's sum in a fixed order; the first warp then does the softmax and the choice
+  __shared__ float s[MOE_MAX_EXPERTS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * MOE_ROUTE_WARPS + warp;
-  if (t >= n_tokens) return;
+  const int t = blockIdx.x;
   const T* x = h + (long long)t * h_stride;
-  float* s = score[warp];
-  for (int e = 0; e < experts; ++e) {
-    const TW* w = w_router + (long long)e * hidden;
+  for (int e = warp; e < experts + (w_shared_gate ? 1 : 0); e += MOE_ROUTE_WARPS) {
+    const TW* w = e < experts ? w_router + (long long)e * hidden : w_shared_gate;
     float dot = 0.0f;
+#pragma unroll 8
     for (int c = lane; c < hidden; c += 32) dot = fmaf(to_float(x[c]), to_float(w[c]), dot);
     dot = warp_sum(dot);
-    if (lane == 0) s[e] = dot;
+    if (lane == 0) {
+      if (e < experts) s[e] = dot;
+      else shared_gate[t] = 1.0f / (1.0f + expf(-dot));
+    }
   }
-  if (w_shared_gate) {
-    float dot = 0.0f;
-    for (int c = lane; c < hidden; c += 32) dot = fmaf(to_float(x[c]), to_float(w_shared_gate[c]), dot);
-    dot = warp_sum(dot);
-    if (lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-dot));
-  }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   float mx = -INFINITY;
   for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, s[e]);
   mx = warp_max(mx);
@@ -82,7 +82,7 @@ extern "C" int llm_moe_route(const void* h, int dtype, long long h_stride, const
                              float* weights, float* shared_gate, int n_tokens, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   LLM_HOST_CHECK(experts >= 1 && experts <= MOE_MAX_EXPERTS && top >= 1 && top <= experts, ERR_BAD_SIZE);
-  const int blocks = (n_tokens + MOE_ROUTE_WARPS - 1) / MOE_ROUTE_WARPS;
+  const int blocks = n_tokens;
 #define ROUTE(T, TW)                                                                                                 \
   launch_kernel(moe_route_kernel<T, TW>, blocks, MOE_ROUTE_WARPS * 32, 0, stream, (const T*)h, h_stride,              \
                 (const TW*)w_router, (const TW*)w_shared_gate, hidden, experts, top, router_scale, ids, weights,        \
@@ -267,6 +267,35 @@ extern "C" int llm_moe_grouped(const void* a, long long a_stride, const void* w,
 }
 
 extern "C" int llm_moe_tile_rows() { return GM_BM; }
+
+// ------------------------------------------------------------------------------ rows in the order of the list
+
+// out[i, :] = a[sorted[i] / top, :] for the `n_slots` places of the list: the tokens' rows, expert by expert,
+// which is the order the tensor-core grouped product reads them in.  16-byte pieces; `width` elements of
+// `esize` bytes make a whole number of them.
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(const uint4* __restrict__ a, long long a_stride16, const int32_t* __restrict__ sorted, int top,
+                       uint4* __restrict__ out, int row16, int n_slots) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long total = (long long)n_slots * row16;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / row16), c = (int)(i % row16);
+    out[i] = a[(long long)(sorted[r] / top) * a_stride16 + c];
+  }
+}
+
+extern "C" int llm_moe_gather_rows(const void* a, long long a_stride_bytes, const int32_t* sorted, int top, void* out,
+                                   int row_bytes, int n_slots, cudaStream_t stream) {
+  if (n_slots <= 0) return 0;
+  LLM_HOST_CHECK(row_bytes > 0 && row_bytes % 16 == 0 && a_stride_bytes % 16 == 0 && top >= 1, ERR_BAD_SIZE);
+  LLM_HOST_CHECK(((uintptr_t)a & 15) == 0 && ((uintptr_t)out & 15) == 0, ERR_BAD_ALIGN);
+  const long long total = (long long)n_slots * (row_bytes / 16);
+  const int blocks = (int)((total + 255) / 256 < 2368 ? (total + 255) / 256 : 2368);
+  launch_kernel(moe_gather_rows_kernel, blocks, 256, 0, stream, (const uint4*)a, a_stride_bytes / 16, sorted, top,
+                (uint4*)out, row_bytes / 16, n_slots);
+  return launch_status();
+}
 
 // ------------------------------------------------------------------------------ combine
 

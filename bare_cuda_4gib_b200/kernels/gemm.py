@@ -31,6 +31,8 @@ def lib(activation: str = "silu"):
         l.llm_gemm_tensor_map.restype = c_int
         l.llm_gemm_bf16.argtypes = [P, P, P, I, I, I, I, L, L, I, I, I, I, I, I, P, I, L, F, F, P, L, P, I, P, L, P, P]
         l.llm_gemm_bf16.restype = c_int
+        l.llm_gemm_grouped_bf16.argtypes = [P, P, P, I, I, I, I, L, I, I, I, I, P, P, P, P, P, P]
+        l.llm_gemm_grouped_bf16.restype = c_int
         _lib = _libs[activation] = l
     return _lib
 

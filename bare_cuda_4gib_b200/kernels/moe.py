@@ -25,21 +25,26 @@ def lib():
         l.llm_moe_grouped.argtypes = [P, L, P, P, I, I, P, P, P, P, I, I, I, I, P]
         l.llm_moe_combine.argtypes = [P, I, P, I, I, L, P, P, I, I, P]
         l.llm_moe_tile_rows.argtypes = []
-        for name in ("llm_moe_route", "llm_moe_sort", "llm_moe_grouped", "llm_moe_combine", "llm_moe_tile_rows"):
+        l.llm_moe_gather_rows.argtypes = [P, L, P, I, P, I, I, P]
+        for name in ("llm_moe_route", "llm_moe_sort", "llm_moe_grouped", "llm_moe_combine", "llm_moe_tile_rows",
+                     "llm_moe_gather_rows"):
             getattr(l, name).restype = c_int
         _lib = l
     return _lib
 
 
-def tile_rows() -> int:
+TENSOR_TILE_ROWS = 128      # rows of a tile of the tensor-core product (its MMA rows)
+
+
+def tile_rows(tensor_cores: bool = False) -> int:
     """Rows of one expert that a block of the grouped products takes."""
-    return int(lib().llm_moe_tile_rows())
+    return TENSOR_TILE_ROWS if tensor_cores else int(lib().llm_moe_tile_rows())
 
 
-def max_tiles(n_slots: int, experts: int) -> int:
+def max_tiles(n_slots: int, experts: int, tensor_cores: bool = False) -> int:
     """The most row tiles `n_slots` slots dealt to `experts` experts can make (a bound that depends
     on the step's shape only, so a captured graph of the step stays valid whatever the router picks)."""
-    return -(-n_slots // tile_rows()) + min(experts, n_slots)
+    return -(-n_slots // tile_rows(tensor_cores)) + min(experts, n_slots)
 
 
 def route(ctx, h: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional[torch.Tensor], top: int,
@@ -55,10 +60,61 @@ def route(ctx, h: torch.Tensor, w_router: torch.Tensor, w_shared_gate: Optional[
 
 
 def sort(ctx, ids: torch.Tensor, n_slots: int, experts: int, sorted_slots: torch.Tensor, tiles: torch.Tensor,
-         n_tiles: torch.Tensor) -> None:
+         n_tiles: torch.Tensor, tensor_cores: bool = False) -> None:
     _dev(ids, sorted_slots, tiles, n_tiles)
-    _check(lib().llm_moe_sort(ids.data_ptr(), n_slots, experts, tile_rows(), sorted_slots.data_ptr(), tiles.data_ptr(),
-                              n_tiles.data_ptr(), ctx.stream), "moe_sort")
+    _check(lib().llm_moe_sort(ids.data_ptr(), n_slots, experts, tile_rows(tensor_cores), sorted_slots.data_ptr(),
+                              tiles.data_ptr(), n_tiles.data_ptr(), ctx.stream), "moe_sort")
+
+
+def gather_rows(ctx, a: torch.Tensor, sorted_slots: torch.Tensor, top: int, out: torch.Tensor, n_slots: int) -> None:
+    """out[i] = a[sorted_slots[i] // top]: the tokens' rows in the order of the list."""
+    _dev(a, sorted_slots, out)
+    if a.dtype != out.dtype or a.stride(1) != 1 or not out.is_contiguous() or out.shape[1] != a.shape[1]:
+        raise TypeError("moe gather_rows: element types or layout not as the kernel needs")
+    es = a.element_size()
+    _check(lib().llm_moe_gather_rows(a.data_ptr(), a.stride(0) * es, sorted_slots.data_ptr(), top, out.data_ptr(),
+                                     a.shape[1] * es, n_slots, ctx.stream), "moe_gather_rows")
+
+
+class GroupedPlan:
+    """Tensor maps of the experts' stacked matrices for the tensor-core grouped product: `w_up`
+    [experts * 2 * ff, hidden] (an expert's gate rows, then its up rows) and `w_down` [experts * hidden, ff]."""
+
+    UP_TILE, DOWN_TILE = 256, 128      # weight rows of a tile (the up tile is half gate rows, half up rows)
+
+    def __init__(self, w_up: torch.Tensor, w_down: torch.Tensor, experts: int):
+        from . import gemm
+        self.experts = experts
+        self.ff, self.hidden = w_down.shape[1], w_down.shape[0] // experts
+        self.up = gemm.GemmPlan(w_up)
+        self.down = gemm.GemmPlan(w_down)
+
+    @staticmethod
+    def takes(w_up: torch.Tensor, w_down: torch.Tensor) -> bool:
+        from . import gemm
+        return gemm.supports(w_up) and gemm.supports(w_down)
+
+
+def grouped_tensor(ctx, plan: GroupedPlan, a: torch.Tensor, out: torch.Tensor, down: bool, sorted_slots: torch.Tensor,
+                   tiles: torch.Tensor, n_tiles: torch.Tensor, weights: torch.Tensor, n_slots: int) -> None:
+    """The grouped products on the tensor cores.  `a` [slots, k] bfloat16 in the order of the list.  up:
+    out [slots, ff] = silu(gate) * up in that order.  down: out float32 [slots, hidden] at the slot's own
+    index, times the slot's weight."""
+    import ctypes
+    from . import gemm
+    _dev(a, out, sorted_slots, tiles, n_tiles, weights)
+    p = plan.down if down else plan.up
+    if a.dtype != torch.bfloat16 or a.stride(1) != 1 or a.shape[1] != p.k or a.data_ptr() % 16 or a.stride(0) % 8:
+        raise TypeError("moe grouped (tensor cores): activations not as the kernel needs")
+    bn = plan.DOWN_TILE if down else plan.UP_TILE
+    n_out = plan.hidden if down else plan.ff
+    err = gemm.error_word(a.device)
+    _check(gemm.lib().llm_gemm_grouped_bf16(
+        ctypes.addressof(p.weight_map(bn if down else bn // 2)), ctypes.addressof(p.act_map(a, gemm.BM)), out.data_ptr(),
+        gemm.DT_F32 if down else gemm.DT_BF16, max_tiles(n_slots, plan.experts, True), n_out, p.k, out.stride(0), bn,
+        0 if down else 1, 0 if down else plan.ff, plan.hidden if down else 2 * plan.ff, tiles.data_ptr(), n_tiles.data_ptr(),
+        sorted_slots.data_ptr() if down else None, weights.data_ptr() if down else None, err.data_ptr(), ctx.stream),
+        "gemm_tcgen05 (grouped)")
 
 
 def grouped(ctx, a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, down: bool, sorted_slots: torch.Tensor,

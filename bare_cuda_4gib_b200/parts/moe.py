@@ -8,8 +8,10 @@
 The experts' matrices are stacked ([experts, 2 * ff, hidden] with an expert's gate rows before its up
 rows, and [experts, hidden, ff]); a step's (token, choice) slots are grouped by expert on the device, and
 two grouped products walk the groups, so no host decision depends on the router and a step is captured
-in a CUDA graph like any other.  A row's sums run over the inner index in order, and a token's slots are
-added in the order of the choice, so a token's result does not depend on what else is in the step.  The
+in a CUDA graph like any other.  bfloat16 steps run both on the tensor cores (the dense product's kernel,
+given the list of row tiles: a tile's rows are one expert's, its weight rows that expert's); float32 steps
+run them in plain arithmetic.  A row of a product depends on that row alone, and a token's slots are added
+in the order of the choice, so a token's result does not depend on what else is in the step.  The
 shared expert runs on the engine's dense products.
 
 params: `hidden`, `experts`, `top`, `router_scale`, `intermediate`, `shared_intermediate` (None: no shared
@@ -77,6 +79,10 @@ class MixtureOfExperts(Part):
             self.shared_down = Linear(t["shared.down"], "moe.shared.down")
             self.shared_gate_up.prepare(dtype)
             self.shared_down.prepare(dtype)
+        from ..kernels.moe import GroupedPlan
+        # bfloat16 experts whose rows the copy engine can fetch run on the tensor cores
+        self.plan = (GroupedPlan(self.w_up, self.w_down, E)
+                     if self.w_up.is_cuda and self.ff % 8 == 0 and GroupedPlan.takes(self.w_up, self.w_down) else None)
         for e in range(E):      # the stacked matrices stand for them from here on
             for n in ("gate", "up", "down"):
                 t.pop(f"e{e}.{n}")
@@ -93,14 +99,26 @@ class MixtureOfExperts(Part):
         sorted_slots = ctx.ws.get("moe_sorted", (n, top), i32)
         # room for every tile a step of this shape can make, three numbers each, and their count
         tiles = ctx.ws.get("moe_tiles", (n, 3 * (top + E) + 1), i32)
-        n_tiles = tiles.view(-1)[3 * M.max_tiles(slots, E):]
+        tc = self.plan is not None and ctx.dtype == torch.bfloat16 and h.dtype == torch.bfloat16
+        n_tiles = tiles.view(-1)[3 * M.max_tiles(slots, E, tc):]
         M.route(ctx, h, self.w_router, self.w_sg, top, self.router_scale, ids, weights, gate, n)
-        M.sort(ctx, ids, slots, E, sorted_slots, tiles, n_tiles)
+        M.sort(ctx, ids, slots, E, sorted_slots, tiles, n_tiles, tc)
         act = ctx.ws.get("moe_act", (n, top * self.ff), ctx.dtype)
-        M.grouped(ctx, h, self.w_up, act, False, sorted_slots, tiles, n_tiles, weights, top, self.ff, self.hidden, slots, E)
+        act_rows = act.view(-1)[: slots * self.ff].view(slots, self.ff)
         y = ctx.ws.get("moe_y", (n, top * self.hidden), f32)
-        M.grouped(ctx, act.view(-1)[: slots * self.ff].view(slots, self.ff), self.w_down, y, True, sorted_slots, tiles,
-                  n_tiles, weights, top, self.hidden, self.ff, slots, E)
+        if tc:
+            # the tokens' rows in the order of the list, so that a tile's rows lie together for the copy engine
+            rows_in = ctx.ws.get("moe_rows", (n, top * self.hidden), ctx.dtype)
+            rows_in = rows_in.view(-1)[: slots * self.hidden].view(slots, self.hidden)
+            M.gather_rows(ctx, h, sorted_slots, top, rows_in, slots)
+            M.grouped_tensor(ctx, self.plan, rows_in, act_rows, False, sorted_slots, tiles, n_tiles, weights, slots)
+            M.grouped_tensor(ctx, self.plan, act_rows, y.view(-1)[: slots * self.hidden].view(slots, self.hidden), True,
+                             sorted_slots, tiles, n_tiles, weights, slots)
+        else:
+            M.grouped(ctx, h, self.w_up, act, False, sorted_slots, tiles, n_tiles, weights, top, self.ff, self.hidden,
+                      slots, E)
+            M.grouped(ctx, act_rows, self.w_down, y, True, sorted_slots, tiles, n_tiles, weights, top, self.hidden, self.ff,
+                      slots, E)
         shared = None
         if self.shared_ff:
             a = self.shared_gate_up.forward(ctx, h, n, ctx.dtype, "moe_shared_act", glu="silu")

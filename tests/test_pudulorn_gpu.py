@@ -122,6 +122,49 @@ def test_grouped_expert_products(dtype, n, experts, top, hidden, ff):
         assert H.row_error(y[slot], want) < tol, (i, slot)
 
 
+@pytest.mark.parametrize("n,experts,top,hidden,ff", [(700, 4, 2, 256, 136), (9, 8, 2, 128, 200), (1, 3, 3, 64, 8),
+                                                      (300, 6, 1, 72, 264), (150, 33, 3, 64, 40)])
+def test_grouped_expert_products_on_tensor_cores(n, experts, top, hidden, ff):
+    """The bfloat16 route: rows put in the list's order, then both grouped products as tiles of 128 rows of one
+    expert (several tiles per expert, a last tile of a few rows, widths that fill no whole tile)."""
+    from bare_cuda_4gib_b200.kernels import gemm, moe as M
+    g = torch.Generator().manual_seed(5)
+    ctx = _stream()
+    bf = torch.bfloat16
+    h = torch.randn(n + 3, hidden + 8, generator=g).to(bf).cuda()[:n, :hidden]      # rows with a stride of their own
+    # a router that prefers low experts, so that the groups differ in size and some may stay empty
+    ids = (torch.rand(n, experts, generator=g) ** 2).argsort(-1)[:, :top].to(torch.int32).cuda()
+    weights = torch.rand(n, top, generator=g).cuda()
+    w_up = (torch.randn(experts * 2 * ff, hidden, generator=g) / hidden ** 0.5).to(bf).cuda()
+    w_down = (torch.randn(experts * hidden, ff, generator=g) / ff ** 0.5).to(bf).cuda()
+    assert M.GroupedPlan.takes(w_up, w_down)
+    plan = M.GroupedPlan(w_up, w_down, experts)
+    slots = n * top
+    sorted_slots = torch.empty(slots, dtype=torch.int32, device="cuda")
+    most = M.max_tiles(slots, experts, True)
+    tiles = torch.zeros(3 * most + 1, dtype=torch.int32, device="cuda")
+    n_tiles = tiles[3 * most:]
+    M.sort(ctx, ids, slots, experts, sorted_slots, tiles, n_tiles, True)
+    assert int(n_tiles) <= most
+    order = sorted_slots.cpu().long()
+    rows_in = torch.full((slots + 5, hidden), float("nan"), dtype=bf, device="cuda")[:slots]   # what lies behind is not read into a result
+    M.gather_rows(ctx, h, sorted_slots, top, rows_in, slots)
+    assert torch.equal(rows_in.cpu(), h.cpu()[order // top])
+    act = torch.full((slots, ff), 7.0, dtype=bf, device="cuda")
+    y = torch.full((slots, hidden), 7.0, device="cuda")
+    M.grouped_tensor(ctx, plan, rows_in, act, False, sorted_slots, tiles, n_tiles, weights, slots)
+    M.grouped_tensor(ctx, plan, act, y, True, sorted_slots, tiles, n_tiles, weights, slots)
+    gemm.check_errors()
+    e_of = ids.view(-1).cpu().long()[order]
+    up3, down3 = w_up.double().cpu().view(experts, 2 * ff, hidden), w_down.double().cpu().view(experts, hidden, ff)
+    gu = torch.einsum("sfk,sk->sf", up3[e_of], h.double().cpu()[order // top])
+    want_act = torch.nn.functional.silu(gu[:, :ff]) * gu[:, ff:]
+    rows_error = lambda got, want: float(((got.double().cpu() - want).abs().amax(-1) / want.abs().amax(-1)).max())
+    assert rows_error(act, want_act) < 3e-2
+    want_y = weights.view(-1).double().cpu()[order, None] * torch.einsum("shf,sf->sh", down3[e_of], act.double().cpu())
+    assert rows_error(y.cpu()[order], want_y) < 1e-2
+
+
 # ------------------------------------------------------------------ every cutting, two configs
 
 @pytest.mark.parametrize("dtype", DTYPES)
