@@ -84,6 +84,19 @@ __device__ __forceinline__ float glu_act(float z) {
 #endif
 }
 
+// What a fused gated product stores for a (gate, up) pair: act(gate) * up, or (a library built with
+// -DGLU_CLAMPED -DGLU_LIMIT=l -DGLU_ALPHA=a) the clamped form g sigmoid(a g) (u + 1) with
+// g = min(gate, l), u = clamp(up, -l, l).
+__device__ __forceinline__ float glu_pair(float gate, float up) {
+#ifdef GLU_CLAMPED
+  const float g = fminf(gate, GLU_LIMIT);
+  const float u = fminf(fmaxf(up, -(GLU_LIMIT)), GLU_LIMIT) + 1.0f;
+  return g / (1.0f + expf(-(GLU_ALPHA) * g)) * u;
+#else
+  return glu_act(gate) * up;
+#endif
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -323,7 +323,7 @@ __device__ __forceinline__ void epilogue_tokens_on_rows(uint32_t lane_base, int 
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       v[j] = __uint_as_float(g[j]) * rs;
-      if (MODE == 1) v[j] = glu_act(v[j]) * (__uint_as_float(u[j]) * rs);
+      if (MODE == 1) v[j] = glu_pair(v[j], __uint_as_float(u[j]) * rs);
     }
     const int f = f0 + c0;
     const long long at = (long long)t_out * ld_out + f;
@@ -632,7 +632,7 @@ gemm_tcgen05_kernel(const Geometry geo, const __grid_constant__ CUtensorMap map_
               const int t = t0 + c0 + j;
               if (t < n_tokens && f < n_features) {
                 const float gate = __uint_as_float(g[j]);
-                const float v = glu_act(gate) * handover[(c0 + j) * 64 + l64];
+                const float v = glu_pair(gate, handover[(c0 + j) * 64 + l64]);
                 if (out_is_f32) out_f32[(long long)t * ld_out + f] = v;
                 else out_bf16[(long long)t * ld_out + f] = __float2bfloat16_rn(v);
               }

@@ -458,7 +458,7 @@ __global__ void __launch_bounds__(THREADS, PRO == PRO_NORM ? 1 : 2) gemv_fused_k
         } else if (EPI == EPI_SWIGLU) {
           const int col = item * 8 + g;
           if (col >= a.n_out) continue;
-          const float val = glu_act(lo_v) * hi_v;
+          const float val = glu_pair(lo_v, hi_v);
           const long long at = (long long)tok * a.out_stride + col;
           if (a.out_dtype == DT_F32) static_cast<float*>(a.out)[at] = val;
           else static_cast<__nv_bfloat16*>(a.out)[at] = __float2bfloat16_rn(val);

@@ -21,6 +21,31 @@
 #define MOE_MAX_EXPERTS 512
 #define MOE_ROUTE_WARPS 4
 
+// A lane's part of x . w over `n` entries, the warp's lanes together covering all of them: 16-byte pieces
+// where both rows allow them (a lane takes every 32nd piece), single entries otherwise.  The order of the
+// sum depends on n and the rows' alignment only.
+template <typename T, typename TW>
+__device__ __forceinline__ float lane_dot(const T* __restrict__ x, const TW* __restrict__ w, int n, int lane) {
+  float dot = 0.0f;
+  constexpr int V = 16 / sizeof(T);
+  if (sizeof(T) == sizeof(TW) && n % V == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
+    const uint4* x4 = reinterpret_cast<const uint4*>(x);
+    const uint4* w4 = reinterpret_cast<const uint4*>(w);
+#pragma unroll 4
+    for (int c = lane; c < n / V; c += 32) {
+      const uint4 xa = x4[c], wa = w4[c];
+      const T* xe = reinterpret_cast<const T*>(&xa);
+      const TW* we = reinterpret_cast<const TW*>(&wa);
+#pragma unroll
+      for (int j = 0; j < V; ++j) dot = fmaf(to_float(xe[j]), to_float(we[j]), dot);
+    }
+    return dot;
+  }
+#pragma unroll 8
+  for (int c = lane; c < n; c += 32) dot = fmaf(to_float(x[c]), to_float(w[c]), dot);
+  return dot;
+}
+
 template <typename T, typename TW>
 __global__ void __launch_bounds__(MOE_ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, long long h_stride, const TW* __restrict__ w_router,
@@ -36,10 +61,7 @@ moe_route_kernel(const T* __restrict__ h, long long h_stride, const TW* __restri
   const T* x = h + (long long)t * h_stride;
   for (int e = warp; e < experts + (w_shared_gate ? 1 : 0); e += MOE_ROUTE_WARPS) {
     const TW* w = e < experts ? w_router + (long long)e * hidden : w_shared_gate;
-    float dot = 0.0f;
-#pragma unroll 8
-    for (int c = lane; c < hidden; c += 32) dot = fmaf(to_float(x[c]), to_float(w[c]), dot);
-    dot = warp_sum(dot);
+    const float dot = warp_sum(lane_dot(x, w, hidden, lane));
     if (lane == 0) {
       if (e < experts) s[e] = dot;
       else shared_gate[t] = 1.0f / (1.0f + expf(-dot));

@@ -12,20 +12,19 @@ import torch
 
 from ..errors import KernelLaunchError
 from . import build
-from .lib import DT_BF16, DT_F32, AddTo, LazyNorm, Partials, Prenormed, _check, _ptr, sm_count
+from .lib import DT_BF16, DT_F32, AddTo, glu_defines, LazyNorm, Partials, Prenormed, _check, _ptr, sm_count
 
 BM, BK = 128, 64
 SPLIT_MAX_ROWS = 256          # steps with more rows never split K
 _libs = {}
 _error_word: Optional[torch.Tensor] = None
-GLU_DEFINES = {"silu": (), "gelu_tanh": ("-DGLU_GELU_TANH",)}      # the gate's activation is a library's own
 
 
 def lib(activation: str = "silu"):
     """The library whose gated products (mode 1) apply `activation` to the gate."""
     _lib = _libs.get(activation)
     if _lib is None:
-        l = build.load_library("gemm_tcgen05.cu", GLU_DEFINES[activation])
+        l = build.load_library("gemm_tcgen05.cu", glu_defines(activation))      # the gate's activation is a library's own
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
         l.llm_gemm_tensor_map.argtypes = [P, P, L, L, L, I]
         l.llm_gemm_tensor_map.restype = c_int

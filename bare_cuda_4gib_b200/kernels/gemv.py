@@ -27,10 +27,10 @@ _smem: Dict[Tuple[int, int], int] = {}
 
 def lib(activation: str = "silu"):
     """The library whose gated products apply `activation` to the gate."""
-    from .gemm import GLU_DEFINES
+    from .lib import glu_defines
     _lib = _libs.get(activation)
     if _lib is None:
-        l = build.load_library("gemv_fused.cu", GLU_DEFINES[activation])
+        l = build.load_library("gemv_fused.cu", glu_defines(activation))
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
         l.llm_gemv_fused_smem.argtypes = [I, I]
         l.llm_gemv_fused_smem.restype = L

@@ -268,10 +268,36 @@ def swiglu(gate_up: Partials, out: torch.Tensor, n_tokens: int, stream=None) -> 
 
 
 GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+CLAMPED_SWISH = "clamped_swish"
+
+
+def clamped_swish(limit: float, alpha: float) -> str:
+    """The name of the clamped gate form with its two constants, g sigmoid(alpha g) (u + 1) with g = min(gate,
+    limit), u = clamp(up, -limit, limit): a gated product is asked for it like for "silu"."""
+    return f"{CLAMPED_SWISH}:{float(limit)!r}:{float(alpha)!r}"
+
+
+def clamped_constants(activation: str):
+    """(limit, alpha) of a name that `clamped_swish` made, None for any other activation."""
+    if not activation.startswith(CLAMPED_SWISH + ":"):
+        return None
+    _, limit, alpha = activation.split(":")
+    return float(limit), float(alpha)
+
+
+def glu_defines(activation: str):
+    """Compiler switches of the library whose fused gated products apply `activation`."""
+    constants = clamped_constants(activation)
+    if constants is not None:
+        return ("-DGLU_CLAMPED", f"-DGLU_LIMIT={constants[0]!r}f", f"-DGLU_ALPHA={constants[1]!r}f")
+    return {"silu": (), "gelu_tanh": ("-DGLU_GELU_TANH",)}[activation]
 
 
 def glu(gate_up: Partials, out: torch.Tensor, n_tokens: int, activation: str, stream=None) -> None:
     """out = activation(gate) * up of [gate | up] (possibly a sum of partial results)."""
+    constants = clamped_constants(activation)
+    if constants is not None:
+        return glu_clamped(gate_up, out, n_tokens, constants[0], constants[1], stream)
     _dev(gate_up.tensor, out)
     _check(plain().lib.llm_glu(gate_up.tensor.data_ptr(), dtype_code(gate_up.tensor.dtype), gate_up.n, gate_up.stride,
                                out.data_ptr(), dtype_code(out.dtype), n_tokens, out.shape[-1],

@@ -81,7 +81,7 @@ class GatedFeedForward(Part):
     gelu).  gate and up are one matrix product against [Wgate; Wup]; the kernels that fuse the
     activation into that product do so for both activations.  A third form, "clamped_swish", bounds
     both factors first: g = min(gate(h), limit), u = clamp(up(h), -limit, limit), and the product is
-    g sigmoid(alpha g) (u + 1); it runs as a kernel of its own behind the [gate; up] product.
+    g sigmoid(alpha g) (u + 1); the products fuse it from a library built with the two constants.
 
     params: `hidden`, `intermediate`, `activation` (, `limit`, `alpha`).  tensors: `gate`, `up`, `down`."""
 
@@ -98,7 +98,8 @@ class GatedFeedForward(Part):
         self.activation = self.params.get("activation", "silu")
         self.clamped = self.activation == "clamped_swish"
         if self.clamped:
-            self.limit, self.alpha = float(self.params["limit"]), float(self.params.get("alpha", 1.0))
+            # the gated products take the form with its two constants like any other activation
+            self.activation = K.clamped_swish(float(self.params["limit"]), float(self.params.get("alpha", 1.0)))
         elif self.activation not in K.GLU_ACTIVATIONS:
             raise KeyError(f"glu feed-forward: activation '{self.activation}' is not one of "
                            f"{sorted(K.GLU_ACTIVATIONS) + ['clamped_swish']}")
@@ -110,10 +111,5 @@ class GatedFeedForward(Part):
 
     def forward(self, ctx, h):
         n = ctx.n_tokens
-        if self.clamped:
-            both = self.gate_up.forward(ctx, h, n, torch.float32 if n <= 256 else ctx.dtype, "ffn_gate_up", allow_partials=True)
-            act = ctx.ws.get("ffn_act", (n, int(self.params["intermediate"])), ctx.dtype)
-            K.glu_clamped(both, act, n, self.limit, self.alpha, ctx.stream)
-            return self.down.forward(ctx, act, n, torch.float32, "ffn_out", allow_partials=True)
         act = self.gate_up.forward(ctx, h, n, ctx.dtype, "ffn_act", glu=self.activation)
         return self.down.forward(ctx, act.tensor, n, torch.float32, "ffn_out", allow_partials=True)
