@@ -170,7 +170,7 @@ extern "C" int llm_diff_attention_plain(const void* q, void* out, const void* ga
 // R / group, head R % group, so a key block loaded once serves every head of the group) and runs
 // both maps: warps 0 .. NW/2-1 the first, the others the second, over the same staged keys and
 // values.  Keys are visited in blocks of 64 positions aligned to absolute positions, copied from
-// the request's pages with cp.async, two blocks in flight.  Two shapes: 4 x 1 warps a map for
+// the request's pages with cp.async, two blocks in flight (up to four for single tokens).  Two shapes: 4 x 1 warps a map for
 // prompts (BM = 64), 1 x 4 for steps of single tokens (BM = 16, each warp 16 of a block's 64
 // keys).  All warps leave (maximum, sum, accumulator) in shared memory; one warp per row then
 // merges them, subtracts, norms, gates and stores.  A block finds its tile by walking the step's
@@ -185,7 +185,14 @@ static_assert(DV % 16 == 0 && DV >= 16 && DV <= 256, "the value size: a multiple
 constexpr int BN = 64;
 constexpr int LDK = 2 * DQ + 8;  // padded rows (conflict-free ldmatrix)
 constexpr int LDV = DV + 8;
-constexpr int STAGES = 2;
+// Key and value blocks in flight: two for prompts (the tensor cores are the limit there); steps of single
+// tokens wait for memory and little else, so they keep as many as fit beside the queries, up to four.
+template <int WARPS_M>
+__host__ __device__ constexpr int stages_of() {
+  if (WARPS_M > 1) return 2;
+  constexpr int fit = (int)((200 * 1024 - 16 * LDK * 2) / (BN * (LDK + LDV) * 2));
+  return fit >= 4 ? 4 : (fit >= 2 ? fit : 2);
+}
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -236,7 +243,7 @@ struct DiffArgs {
 template <int WARPS_M, int WARPS_N>
 constexpr size_t diff_smem_bytes() {
   constexpr int BM = 16 * WARPS_M;
-  constexpr size_t stages = (size_t)STAGES * BN * (LDK + LDV) * 2;
+  constexpr size_t stages = (size_t)stages_of<WARPS_M>() * BN * (LDK + LDV) * 2;
   constexpr size_t merge = (size_t)2 * WARPS_N * BM * (DV + 2) * 4;
   return (size_t)BM * LDK * 2 + (stages > merge ? stages : merge);
 }
@@ -247,6 +254,7 @@ diff_attention_mma_kernel(DiffArgs a) {
   constexpr int NW = 2 * WARPS_M * WARPS_N, NT_THREADS = NW * 32;
   constexpr int BM = 16 * WARPS_M;
   constexpr int KEYS_W = BN / WARPS_N, NT = KEYS_W / 8;
+  constexpr int STAGES = stages_of<WARPS_M>();
   constexpr int KCH = 2 * DQ / 8, VCH = DV / 8;  // 16-byte chunks per key and value row
 
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -327,7 +335,8 @@ diff_attention_mma_kernel(DiffArgs a) {
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  load_block(kb_begin, 0);
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) load_block(kb_begin + i, i);   // (a group each, empty behind the last block)
   __syncthreads();  // Q staged
 
   uint32_t qf[DQ / 16][4];
@@ -351,9 +360,9 @@ diff_attention_mma_kernel(DiffArgs a) {
 
   for (int kb = kb_begin; kb < kb_end; ++kb) {
     const int stage = (kb - kb_begin) % STAGES;
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncthreads();  // block kb has landed; everyone is done with the other stage
-    load_block(kb + 1, (kb - kb_begin + 1) % STAGES);
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2) : "memory");
+    __syncthreads();  // block kb has landed; everyone is done with block kb - 1, whose stage is filled next
+    load_block(kb + STAGES - 1, (kb - kb_begin + STAGES - 1) % STAGES);
     const __nv_bfloat16* ks_ = Ks + stage * BN * LDK;
     const __nv_bfloat16* vs_ = Vs + stage * BN * LDV;
     const int key0 = kb * BN + wn * KEYS_W;
