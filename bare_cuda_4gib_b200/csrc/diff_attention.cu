@@ -316,17 +316,23 @@ diff_attention_mma_kernel(DiffArgs a) {
       __nv_bfloat16* ks = Ks + stage * BN * LDK;
       __nv_bfloat16* vs = Vs + stage * BN * LDV;
       const int key0 = kb * BN;
-      for (int i = threadIdx.x; i < BN * (KCH + VCH); i += NT_THREADS) {
+      // a thread's 16-byte pieces of the block: first the pages of all of them (independent loads), then the copies
+      constexpr int PIECES = (BN * (KCH + VCH) + NT_THREADS - 1) / NT_THREADS;
+      int page[PIECES];
+#pragma unroll
+      for (int j = 0; j < PIECES; ++j) {
+        const int key = key0 + (threadIdx.x + j * NT_THREADS) / (KCH + VCH);
+        page[j] = key < kv_len ? __ldg(table_row + key / page_tokens) : -1;
+      }
+#pragma unroll
+      for (int j = 0; j < PIECES; ++j) {
+        const int i = threadIdx.x + j * NT_THREADS;
+        if (i >= BN * (KCH + VCH)) break;
         const int r = i / (KCH + VCH), c = i % (KCH + VCH);
         const int key = key0 + r;
-        bool valid = key < kv_len;
-        long long in_page = 0, page_base = 0;
-        if (valid) {
-          const int page = __ldg(table_row + key / page_tokens);
-          valid = page >= 0;
-          page_base = (long long)page * a.cache.page_stride;
-          in_page = (long long)kvh * page_tokens + (key % page_tokens);
-        }
+        const bool valid = page[j] >= 0;
+        const long long page_base = valid ? (long long)page[j] * a.cache.page_stride : 0;
+        const long long in_page = valid ? (long long)kvh * page_tokens + (key % page_tokens) : 0;
         if (c < KCH)
           cp_async16(ks + r * LDK + c * 8, kc + (valid ? page_base + in_page * (2 * DQ) + c * 8 : 0), valid);
         else
