@@ -174,14 +174,15 @@ extern "C" int llm_conv_ring_write(const void* u, int dtype, long long u_stride,
 
 // One warp per (row, query head).  Keys are walked in blocks of 32 absolute positions (block b
 // holds positions 32 b .. 32 b + 31), one key per lane: score = (q . k) * scale +
-// bias[head][distance]; online softmax over blocks; the value sum with one output channel group
+// bias[head][distance] (with `softcap` > 0 the scaled score first becomes softcap * tanh(score / softcap));
+// online softmax over blocks; the value sum with one output channel group
 // per lane.  Each sum's order depends on the sizes and on absolute key positions only.
 template <typename T>
 __global__ void __launch_bounds__(BA_WARPS * 32)
 biased_attention_kernel(const T* __restrict__ q, T* __restrict__ out, long long out_stride, PagedCacheKV cache,
                         const float* __restrict__ bias, int bias_len, const int32_t* __restrict__ positions,
                         const int32_t* __restrict__ row_seq, int q_heads, int n_tokens, float scale, int window,
-                        float out_scale) {
+                        float out_scale, float softcap) {
   pdl_launch_dependents();
   extern __shared__ float q_sm[];   // [BA_WARPS][k_dim]
   const int dk = cache.k_dim, dv = cache.v_dim;
@@ -213,6 +214,7 @@ biased_attention_kernel(const T* __restrict__ q, T* __restrict__ out, long long 
       float dot = 0.0f;
       for (int d = 0; d < dk; ++d) dot += qs[d] * to_float(kr[d]);
       s = dot * scale;
+      if (softcap > 0.0f) s = softcap * tanhf(s / softcap);
       if (bias_h) s += bias_h[min(p - key, bias_len - 1)];
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -248,7 +250,7 @@ extern "C" int llm_biased_attention(const void* q, void* out, int dtype, long lo
                                     void* cache_v, const int32_t* block_table, long long page_stride, int table_stride,
                                     int page_tokens, int kv_heads, int k_dim, int v_dim, const float* bias, int bias_len,
                                     const int32_t* positions, const int32_t* row_seq, int q_heads, int n_tokens,
-                                    float scale, int window, float out_scale, cudaStream_t stream) {
+                                    float scale, int window, float out_scale, float softcap, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   LLM_HOST_CHECK(v_dim <= 256 && k_dim >= 1 && kv_heads >= 1 && q_heads % kv_heads == 0, ERR_BAD_SIZE);
   LLM_HOST_CHECK(bias == nullptr || bias_len >= 1, ERR_BAD_SIZE);
@@ -259,11 +261,11 @@ extern "C" int llm_biased_attention(const void* q, void* out, int dtype, long lo
   const int blocks = (int)((items + BA_WARPS - 1) / BA_WARPS);
   if (dtype == DT_F32)
     launch_kernel(biased_attention_kernel<float>, blocks, BA_WARPS * 32, smem, stream, (const float*)q, (float*)out,
-                  out_stride, cache, bias, bias_len, positions, row_seq, q_heads, n_tokens, scale, window, out_scale);
+                  out_stride, cache, bias, bias_len, positions, row_seq, q_heads, n_tokens, scale, window, out_scale, softcap);
   else if (dtype == DT_BF16)
     launch_kernel(biased_attention_kernel<__nv_bfloat16>, blocks, BA_WARPS * 32, smem, stream, (const __nv_bfloat16*)q,
                   (__nv_bfloat16*)out, out_stride, cache, bias, bias_len, positions, row_seq, q_heads, n_tokens, scale,
-                  window, out_scale);
+                  window, out_scale, softcap);
   else
     return ERR_BAD_DTYPE;
   return launch_status();

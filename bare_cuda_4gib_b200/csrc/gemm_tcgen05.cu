@@ -324,6 +324,14 @@ __device__ __forceinline__ void epilogue_tokens_on_rows(uint32_t lane_base, int 
     for (int j = 0; j < 16; ++j) {
       v[j] = __uint_as_float(g[j]) * rs;
       if (MODE == 1) v[j] = glu_pair(v[j], __uint_as_float(u[j]) * rs);
+#ifdef GROUPED_UP_RELU2
+      // a library built with -DGROUPED_UP_RELU2: a grouped product that keeps its rows in place (the up
+      // product of ungated experts) stores relu(x)^2
+      if (MODE == 0 && ex.group_tiles && !ex.row_map) {
+        const float r = fmaxf(v[j], 0.0f);
+        v[j] = r * r;
+      }
+#endif
     }
     const int f = f0 + c0;
     const long long at = (long long)t_out * ld_out + f;

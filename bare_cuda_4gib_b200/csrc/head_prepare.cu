@@ -9,6 +9,10 @@
 // (the maps of differential attention), each normed and turned by itself; the values belong to the head.  q goes
 // to its buffer, k into the request's cache page, and the values - a projection of their own, or
 // the keys as projected, before norm and rotation - beside it.  Grid (token, share of the token's heads).  Norm, angle and rotation are float32.
+// `bias` (float32, indexed by the projection's column, or null) is added to q, k and v as they are read.
+// Value mixing: with `v_mix_in` [tokens, kv_heads * v_dim] float32 the value becomes (1 - v_mix) v + v_mix *
+// v_mix_in (another layer's values of the same token), and with `v_mix_out` the value as cached is also
+// left there in float32 for later layers of the same step.
 // Also here: the sigmoid gate on a mixer's output.
 
 #include "common.cuh"
@@ -23,7 +27,9 @@ headnorm_rope_cache_kernel(const T* __restrict__ u, long long u_stride, int q_co
                            const TW* __restrict__ q_norm_w, const TW* __restrict__ k_norm_w, float eps,
                            const float* __restrict__ inv_freq, int rot_dims, int halves, int maps, float mag,
                            T* __restrict__ q_out, PagedCache cache, int v_dim, const int32_t* __restrict__ positions,
-                           const int32_t* __restrict__ row_seq, int q_heads, int write_cache) {
+                           const int32_t* __restrict__ row_seq, int q_heads, int write_cache,
+                           const float* __restrict__ bias, const float* __restrict__ v_mix_in, float v_mix,
+                           float* __restrict__ v_mix_out) {
   pdl_launch_dependents();
   pdl_wait();
   extern __shared__ float head_smem[];  // PREP_WARPS * head_dim
@@ -39,6 +45,7 @@ headnorm_rope_cache_kernel(const T* __restrict__ u, long long u_stride, int q_co
     const int h = unit / maps, map = unit - h * maps;
     const T* x = row + (is_q ? q_col : k_col) + (long long)unit * d;
     const TW* w = is_q ? q_norm_w : k_norm_w;
+    const float* bx = bias ? bias + (is_q ? q_col : k_col) + (long long)unit * d : nullptr;
     T* dst = nullptr;
     if (is_q) {
       dst = q_out + ((long long)t * q_heads * maps + unit) * d;
@@ -50,14 +57,25 @@ headnorm_rope_cache_kernel(const T* __restrict__ u, long long u_stride, int q_co
         if (map == 0) {
           T* vdst = (T*)cache.v + (long long)page * cache.page_stride + slot * v_dim;
           const T* vx = v_col >= 0 ? row + v_col + h * v_dim : x;
-          for (int c = lane; c < v_dim; c += 32) vdst[c] = vx[c];
+          if (!bias && !v_mix_in && !v_mix_out) {
+            for (int c = lane; c < v_dim; c += 32) vdst[c] = vx[c];
+          } else {
+            const float* bv = bias ? (v_col >= 0 ? bias + v_col + h * v_dim : bx) : nullptr;
+            const long long at = ((long long)t * cache.kv_heads + h) * v_dim;
+            for (int c = lane; c < v_dim; c += 32) {
+              float v = to_float(vx[c]) + (bv ? bv[c] : 0.0f);
+              if (v_mix_in) v = (1.0f - v_mix) * v + v_mix * v_mix_in[at + c];
+              if (v_mix_out) v_mix_out[at + c] = v;
+              vdst[c] = from_float<T>(v);
+            }
+          }
         }
       }
     }
     if (!dst) continue;      // the whole warp takes the same way
     float sq = 0.0f;
     for (int c = lane; c < d; c += 32) {
-      const float v = to_float(x[c]);
+      const float v = to_float(x[c]) + (bx ? bx[c] : 0.0f);
       s[c] = v;
       sq += v * v;
     }
@@ -88,6 +106,7 @@ extern "C" int llm_headnorm_rope_cache(const void* u, int dtype, long long u_str
                                        const int32_t* block_table, long long page_stride, int table_stride,
                                        int page_tokens, int kv_heads, int head_dim, int v_dim, const int32_t* positions,
                                        const int32_t* row_seq, int q_heads, int write_cache, int n_tokens,
+                                       const float* bias, const float* v_mix_in, float v_mix, float* v_mix_out,
                                        cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   LLM_HOST_CHECK(maps >= 1 && head_dim % maps == 0, ERR_BAD_SIZE);
@@ -102,12 +121,13 @@ extern "C" int llm_headnorm_rope_cache(const void* u, int dtype, long long u_str
   if (dtype == DT_F32)
     launch_kernel(headnorm_rope_cache_kernel<float, float>, grid, PREP_WARPS * 32, smem, stream, (const float*)u,
                   u_stride, q_col, k_col, v_col, (const float*)q_norm_w, (const float*)k_norm_w, eps, inv_freq, rot_dims,
-                  halves, maps, mag, (float*)q_out, c, v_dim, positions, row_seq, q_heads, write_cache);
+                  halves, maps, mag, (float*)q_out, c, v_dim, positions, row_seq, q_heads, write_cache, bias, v_mix_in, v_mix,
+                  v_mix_out);
   else if (dtype == DT_BF16)
     launch_kernel(headnorm_rope_cache_kernel<__nv_bfloat16, __nv_bfloat16>, grid, PREP_WARPS * 32, smem, stream,
                   (const __nv_bfloat16*)u, u_stride, q_col, k_col, v_col, (const __nv_bfloat16*)q_norm_w,
                   (const __nv_bfloat16*)k_norm_w, eps, inv_freq, rot_dims, halves, maps, mag, (__nv_bfloat16*)q_out, c, v_dim,
-                  positions, row_seq, q_heads, write_cache);
+                  positions, row_seq, q_heads, write_cache, bias, v_mix_in, v_mix, v_mix_out);
   else
     return ERR_BAD_DTYPE;
   return launch_status();

@@ -50,12 +50,15 @@ template <typename T, typename TW>
 __global__ void __launch_bounds__(MOE_ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, long long h_stride, const TW* __restrict__ w_router,
                  const TW* __restrict__ w_shared_gate, int hidden, int experts, int top, float router_scale,
-                 int32_t* __restrict__ ids, float* __restrict__ weights, float* __restrict__ shared_gate, int n_tokens) {
+                 int32_t* __restrict__ ids, float* __restrict__ weights, float* __restrict__ shared_gate, int n_tokens,
+                 const float* __restrict__ correction, int groups, int keep) {
   pdl_launch_dependents();
   pdl_wait();
   // a block per token: its warps share the experts' dot products (and the shared gate's, counted as one
   // more), each a warp's sum in a fixed order; the first warp then does the softmax and the choice
   __shared__ float s[MOE_MAX_EXPERTS];
+  __shared__ float choice[MOE_MAX_EXPERTS];      // what the choice goes by; a chosen or barred expert holds -inf
+  __shared__ float group_best[MOE_MAX_EXPERTS];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
   const T* x = h + (long long)t * h_stride;
@@ -80,20 +83,58 @@ moe_route_kernel(const T* __restrict__ h, long long h_stride, const TW* __restri
   }
   sum = warp_sum(sum);
   __syncwarp();
+  // the score is the softmax; the choice goes by score + correction (where the router has one)
+  for (int e = lane; e < experts; e += 32) {
+    const float p = s[e] / sum;
+    s[e] = p;
+    choice[e] = correction ? p + correction[e] : p;
+  }
+  __syncwarp();
+  if (groups > 1 && keep < groups) {
+    // experts form `groups` equal groups of neighbours; a group counts by its best choice value, and only
+    // the `keep` best groups stay eligible (the lowest index wins a tie)
+    const int size = experts / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float best = -INFINITY;
+      for (int e = g * size; e < (g + 1) * size; ++e) best = fmaxf(best, choice[e]);
+      group_best[g] = best;
+    }
+    __syncwarp();
+    for (int k = 0; k < keep; ++k) {
+      float best = -INFINITY;
+      int at = groups;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = group_best[g];
+        if (isnan(v)) continue;      // kept already
+        if (at == groups || v > best) best = v, at = g;
+      }
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (oa < groups && (at == groups || ob > best || (ob == best && oa < at))) best = ob, at = oa;
+      }
+      if (lane == 0 && at < groups) group_best[at] = NAN;      // kept: marked, and out of the running
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (!isnan(group_best[e / size])) choice[e] = -INFINITY;
+    __syncwarp();
+  }
   for (int k = 0; k < top; ++k) {
-    float best = -1.0f;
+    float best = -INFINITY;
     int at = experts;
     for (int e = lane; e < experts; e += 32)
-      if (s[e] > best) best = s[e], at = e;      // ascending e: the lowest index of a lane's ties stays
+      if (at == experts ? choice[e] > -INFINITY : choice[e] > best) best = choice[e], at = e;      // ascending e: the lowest index of a lane's ties stays
     for (int o = 16; o > 0; o >>= 1) {
       const float ob = __shfl_xor_sync(0xffffffffu, best, o);
       const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-      if (ob > best || (ob == best && oa < at)) best = ob, at = oa;
+      if (oa < experts && (at == experts || ob > best || (ob == best && oa < at))) best = ob, at = oa;
     }
+    if (at >= experts) at = 0;      // fewer eligible experts than choices: cannot happen with a checked configuration
     if (lane == 0) {
       ids[(long long)t * top + k] = at;
-      weights[(long long)t * top + k] = best / sum * router_scale;
-      s[at] = -2.0f;
+      weights[(long long)t * top + k] = s[at] * router_scale;
+      choice[at] = -INFINITY;
     }
     __syncwarp();
   }
@@ -101,14 +142,17 @@ moe_route_kernel(const T* __restrict__ h, long long h_stride, const TW* __restri
 
 extern "C" int llm_moe_route(const void* h, int dtype, long long h_stride, const void* w_router, const void* w_shared_gate,
                              int w_dtype, int hidden, int experts, int top, float router_scale, int32_t* ids,
-                             float* weights, float* shared_gate, int n_tokens, cudaStream_t stream) {
+                             float* weights, float* shared_gate, int n_tokens, const float* correction, int groups,
+                             int keep, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   LLM_HOST_CHECK(experts >= 1 && experts <= MOE_MAX_EXPERTS && top >= 1 && top <= experts, ERR_BAD_SIZE);
+  LLM_HOST_CHECK(groups <= 1 || (experts % groups == 0 && keep >= 1 && keep <= groups && top <= keep * (experts / groups)),
+                 ERR_BAD_SIZE);
   const int blocks = n_tokens;
 #define ROUTE(T, TW)                                                                                                 \
   launch_kernel(moe_route_kernel<T, TW>, blocks, MOE_ROUTE_WARPS * 32, 0, stream, (const T*)h, h_stride,              \
                 (const TW*)w_router, (const TW*)w_shared_gate, hidden, experts, top, router_scale, ids, weights,        \
-                shared_gate, n_tokens)
+                shared_gate, n_tokens, correction, groups, keep)
   if (dtype == DT_F32 && w_dtype == DT_F32) ROUTE(float, float);
   else if (dtype == DT_BF16 && w_dtype == DT_BF16) ROUTE(__nv_bfloat16, __nv_bfloat16);
   else if (dtype == DT_BF16 && w_dtype == DT_F32) ROUTE(__nv_bfloat16, float);
@@ -128,12 +172,14 @@ extern "C" int llm_moe_route(const void* h, int dtype, long long h_stride, const
 __global__ void __launch_bounds__(MOE_SORT_THREADS)
 moe_sort_kernel(const int32_t* __restrict__ ids, int n_slots, int experts, int tile_rows, int32_t* __restrict__ sorted,
                 int32_t* __restrict__ tiles, int32_t* __restrict__ n_tiles) {
+  // (`experts` counts the experts that have matrices: a slot whose id lies beyond them is listed nowhere)
   pdl_launch_dependents();
   pdl_wait();
   __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS + 1], tile_start[MOE_MAX_EXPERTS + 1];
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < n_slots; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+  for (int i = threadIdx.x; i < n_slots; i += blockDim.x)
+    if (ids[i] < experts) atomicAdd(&count[ids[i]], 1);
   __syncthreads();
   if (threadIdx.x == 0) {
     int at = 0, tl = 0;
@@ -148,6 +194,8 @@ moe_sort_kernel(const int32_t* __restrict__ ids, int n_slots, int experts, int t
     *n_tiles = tl;
   }
   __syncthreads();
+  // places past the last listed slot name slot 0, so that whatever walks the whole list reads valid rows
+  for (int i = start[experts] + threadIdx.x; i < n_slots; i += blockDim.x) sorted[i] = 0;
   // a warp per expert walks the slots in order, so the places inside an expert ascend with the slot
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
   for (int e = warp; e < experts; e += n_warps) {
@@ -181,14 +229,15 @@ extern "C" int llm_moe_sort(const int32_t* ids, int n_slots, int experts, int ti
 
 // SIMT form, any element type.  A block takes one tile of rows (one expert) and GM_BN output columns.
 //   UP   (DOWN = false): row r of the tile is token sorted[first + r] / top of `a` [tokens, k];
-//        w [experts][2 * n][k] (gate rows, then up rows); out[first + r, c] = act(gate) * up, [slots, n].
+//        GATED: w [experts][2 * n][k] (gate rows, then up rows); out[first + r, c] = act(gate) * up, [slots, n];
+//        otherwise w [experts][n][k] and out[first + r, c] = relu(up)^2.
 //   DOWN (DOWN = true):  row r is row first + r of `a` [slots, k]; w [experts][n][k];
 //        out[sorted[first + r], c] = weight[sorted[first + r]] * sum, float32 [slots, n].
 #define GM_BM 32
 #define GM_BN 64
 #define GM_BK 16
 
-template <typename T, bool DOWN>
+template <typename T, bool DOWN, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const T* __restrict__ a, long long a_stride, const T* __restrict__ w, void* __restrict__ out_,
                    const int32_t* __restrict__ sorted, const int32_t* __restrict__ tiles,
@@ -200,7 +249,7 @@ moe_grouped_kernel(const T* __restrict__ a, long long a_stride, const T* __restr
   const int n0 = blockIdx.y * GM_BN;
   __shared__ float As[GM_BK][GM_BM + 1];
   __shared__ float Wg[GM_BK][GM_BN + 1];
-  __shared__ float Wu[DOWN ? 1 : GM_BK][GM_BN + 1];
+  __shared__ float Wu[GATED ? GM_BK : 1][GM_BN + 1];
   __shared__ int row_src[GM_BM];
   if (threadIdx.x < GM_BM) {
     const int r = threadIdx.x;
@@ -209,7 +258,7 @@ moe_grouped_kernel(const T* __restrict__ a, long long a_stride, const T* __restr
     row_src[r] = src;
   }
   __syncthreads();
-  const T* wg = w + (long long)expert * (DOWN ? 1 : 2) * n * k;
+  const T* wg = w + (long long)expert * (GATED ? 2 : 1) * n * k;
   const T* wu = wg + (long long)n * k;
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;      // columns tx * 4 .., rows ty * 2 ..
   float acc_g[2][4] = {}, acc_u[2][4] = {};
@@ -223,7 +272,7 @@ moe_grouped_kernel(const T* __restrict__ a, long long a_stride, const T* __restr
       const int r = i / GM_BK, c = i % GM_BK;
       const bool ok = n0 + r < n && k0 + c < k;
       Wg[c][r] = ok ? to_float(wg[(long long)(n0 + r) * k + k0 + c]) : 0.0f;
-      if (!DOWN) Wu[c][r] = ok ? to_float(wu[(long long)(n0 + r) * k + k0 + c]) : 0.0f;
+      if (GATED) Wu[c][r] = ok ? to_float(wu[(long long)(n0 + r) * k + k0 + c]) : 0.0f;
     }
     __syncthreads();
 #pragma unroll
@@ -234,14 +283,14 @@ moe_grouped_kernel(const T* __restrict__ a, long long a_stride, const T* __restr
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         gv[j] = Wg[c][tx * 4 + j];
-        if (!DOWN) uv[j] = Wu[c][tx * 4 + j];
+        if (GATED) uv[j] = Wu[c][tx * 4 + j];
       }
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           acc_g[i][j] = fmaf(av[i], gv[j], acc_g[i][j]);
-          if (!DOWN) acc_u[i][j] = fmaf(av[i], uv[j], acc_u[i][j]);
+          if (GATED) acc_u[i][j] = fmaf(av[i], uv[j], acc_u[i][j]);
         }
     }
     __syncthreads();
@@ -263,7 +312,8 @@ moe_grouped_kernel(const T* __restrict__ a, long long a_stride, const T* __restr
       for (int j = 0; j < 4; ++j)
         if (n0 + tx * 4 + j < n) {
           const float g = acc_g[i][j];
-          out[n0 + tx * 4 + j] = from_float<T>(g / (1.0f + expf(-g)) * acc_u[i][j]);
+          const float r = fmaxf(g, 0.0f);
+          out[n0 + tx * 4 + j] = from_float<T>(GATED ? g / (1.0f + expf(-g)) * acc_u[i][j] : r * r);
         }
     }
   }
@@ -271,16 +321,18 @@ moe_grouped_kernel(const T* __restrict__ a, long long a_stride, const T* __restr
 
 extern "C" int llm_moe_grouped(const void* a, long long a_stride, const void* w, void* out, int dtype, int down,
                                const int32_t* sorted, const int32_t* tiles, const int32_t* n_tiles, const float* weights,
-                               int top, int n, int k, int max_tiles, cudaStream_t stream) {
+                               int top, int n, int k, int max_tiles, int gated, cudaStream_t stream) {
   if (max_tiles <= 0) return 0;
   const dim3 grid(max_tiles, (n + GM_BN - 1) / GM_BN);
-#define GROUPED(T, DOWN)                                                                                            \
-  launch_kernel(moe_grouped_kernel<T, DOWN>, grid, 256, 0, stream, (const T*)a, a_stride, (const T*)w, out, sorted, \
-                tiles, n_tiles, weights, top, n, k)
+#define GROUPED(T, DOWN, GATED)                                                                                     \
+  launch_kernel(moe_grouped_kernel<T, DOWN, GATED>, grid, 256, 0, stream, (const T*)a, a_stride, (const T*)w, out,  \
+                sorted, tiles, n_tiles, weights, top, n, k)
   if (dtype == DT_F32) {
-    if (down) GROUPED(float, true); else GROUPED(float, false);
+    if (down) GROUPED(float, true, false); else if (gated) GROUPED(float, false, true); else GROUPED(float, false, false);
   } else if (dtype == DT_BF16) {
-    if (down) GROUPED(__nv_bfloat16, true); else GROUPED(__nv_bfloat16, false);
+    if (down) GROUPED(__nv_bfloat16, true, false);
+    else if (gated) GROUPED(__nv_bfloat16, false, true);
+    else GROUPED(__nv_bfloat16, false, false);
   } else {
     return ERR_BAD_DTYPE;
   }
@@ -322,17 +374,22 @@ extern "C" int llm_moe_gather_rows(const void* a, long long a_stride_bytes, cons
 // ------------------------------------------------------------------------------ combine
 
 // out[t, c] = sum_k y[t * top + k, c]  (+ shared_gate[t] * sum_p shared[p][t, c]), float32.
-template <typename TS>
+// With `ids`: a slot whose expert lies beyond `experts` is an identity expert, its result weight * h[t].
+template <typename TS, typename TH>
 __global__ void moe_combine_kernel(const float* __restrict__ y, int top, const TS* __restrict__ shared, int n_partials,
                                    long long partial_stride, const float* __restrict__ shared_gate,
-                                   float* __restrict__ out, long long total, int hidden) {
+                                   float* __restrict__ out, long long total, int hidden, const int32_t* __restrict__ ids,
+                                   const float* __restrict__ weights, int experts, const TH* __restrict__ h,
+                                   long long h_stride) {
   pdl_launch_dependents();
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long t = i / hidden;
     const int c = (int)(i - t * hidden);
     float sum = 0.0f;
-    for (int k = 0; k < top; ++k) sum += y[(t * top + k) * hidden + c];
+    for (int k = 0; k < top; ++k)
+      sum += (ids && ids[t * top + k] >= experts) ? weights[t * top + k] * to_float(h[t * h_stride + c])
+                                                  : y[(t * top + k) * hidden + c];
     if (shared) {
       float sh = 0.0f;
       for (int p = 0; p < n_partials; ++p) sh += to_float(shared[p * partial_stride + i]);
@@ -344,17 +401,24 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, int top, const T
 
 extern "C" int llm_moe_combine(const float* y, int top, const void* shared, int shared_dtype, int n_partials,
                                long long partial_stride, const float* shared_gate, float* out, int n_tokens, int hidden,
-                               cudaStream_t stream) {
+                               const int32_t* ids, const float* weights, int experts, const void* h, int h_dtype,
+                               long long h_stride, cudaStream_t stream) {
   const long long total = (long long)n_tokens * hidden;
   if (total <= 0) return 0;
+  LLM_HOST_CHECK(!ids || (weights && h), ERR_BAD_SIZE);
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-  if (!shared || shared_dtype == DT_F32)
-    launch_kernel(moe_combine_kernel<float>, blocks, 256, 0, stream, y, top, (const float*)shared, n_partials,
-                  partial_stride, shared_gate, out, total, hidden);
-  else if (shared_dtype == DT_BF16)
-    launch_kernel(moe_combine_kernel<__nv_bfloat16>, blocks, 256, 0, stream, y, top, (const __nv_bfloat16*)shared,
-                  n_partials, partial_stride, shared_gate, out, total, hidden);
-  else
+#define COMBINE(TS, TH)                                                                                              \
+  launch_kernel(moe_combine_kernel<TS, TH>, blocks, 256, 0, stream, y, top, (const TS*)shared, n_partials,           \
+                partial_stride, shared_gate, out, total, hidden, ids, weights, experts, (const TH*)h, h_stride)
+  const bool hf = !ids || h_dtype == DT_F32;
+  if (ids && h_dtype != DT_F32 && h_dtype != DT_BF16) return ERR_BAD_DTYPE;
+  if (!shared || shared_dtype == DT_F32) {
+    if (hf) COMBINE(float, float); else COMBINE(float, __nv_bfloat16);
+  } else if (shared_dtype == DT_BF16) {
+    if (hf) COMBINE(__nv_bfloat16, float); else COMBINE(__nv_bfloat16, __nv_bfloat16);
+  } else {
     return ERR_BAD_DTYPE;
+  }
+#undef COMBINE
   return launch_status();
 }

@@ -33,17 +33,22 @@ embed_rmsnorm_kernel(const TT* __restrict__ table, const int32_t* __restrict__ i
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = row_cache[i] * scale * to_float(weight[i]);
 }
 
-extern "C" int llm_embed_rmsnorm(const void* table, const int32_t* ids, const void* weight, int dtype, float* out,
-                                 int n_tokens, int hidden, float eps, cudaStream_t stream) {
+// dtype: the table's element type; weight_dtype: the norm weight's (the table's, or float32 for a factor
+// that was formed in float32).
+extern "C" int llm_embed_rmsnorm(const void* table, const int32_t* ids, const void* weight, int dtype, int weight_dtype,
+                                 float* out, int n_tokens, int hidden, float eps, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   const size_t smem = (size_t)(hidden + 32) * sizeof(float);
   LLM_HOST_CHECK(smem <= 48 * 1024, ERR_BAD_SIZE);
-  if (dtype == DT_F32)
+  if (dtype == DT_F32 && weight_dtype == DT_F32)
     launch_kernel(embed_rmsnorm_kernel<float, float>, n_tokens, NORM_THREADS, smem, stream, (const float*)table, ids,
                   (const float*)weight, out, hidden, eps);
-  else if (dtype == DT_BF16)
+  else if (dtype == DT_BF16 && weight_dtype == DT_BF16)
     launch_kernel(embed_rmsnorm_kernel<__nv_bfloat16, __nv_bfloat16>, n_tokens, NORM_THREADS, smem, stream,
                   (const __nv_bfloat16*)table, ids, (const __nv_bfloat16*)weight, out, hidden, eps);
+  else if (dtype == DT_BF16 && weight_dtype == DT_F32)
+    launch_kernel(embed_rmsnorm_kernel<__nv_bfloat16, float>, n_tokens, NORM_THREADS, smem, stream,
+                  (const __nv_bfloat16*)table, ids, (const float*)weight, out, hidden, eps);
   else
     return ERR_BAD_DTYPE;
   return launch_status();

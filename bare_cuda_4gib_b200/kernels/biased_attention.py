@@ -23,7 +23,7 @@ def lib():
         l.llm_conv_norm_cache.argtypes = [P, I, L, P, I, P, P, P, P, P, P, P, L, I, I, I, I, I, P, P, P, P, I, I, F, F,
                                           I, I, P]
         l.llm_conv_ring_write.argtypes = [P, I, L, P, I, I, P, P, P, P, I, P]
-        l.llm_biased_attention.argtypes = [P, P, I, L, P, P, P, L, I, I, I, I, I, P, I, P, P, I, I, F, I, F, P]
+        l.llm_biased_attention.argtypes = [P, P, I, L, P, P, P, L, I, I, I, I, I, P, I, P, P, I, I, F, I, F, F, P]
         for name in ("llm_conv_norm_cache", "llm_conv_ring_write", "llm_biased_attention"):
             getattr(l, name).restype = c_int
         _lib = l
@@ -54,14 +54,15 @@ def conv_ring_write(ctx, u: torch.Tensor, ring: torch.Tensor, taps: int, channel
 
 
 def attention(ctx, q: torch.Tensor, out: torch.Tensor, cache: CacheView, bias: Optional[torch.Tensor], q_heads: int,
-              scale: float, window: int = 0, out_scale: float = 1.0) -> None:
+              scale: float, window: int = 0, out_scale: float = 1.0, softcap: float = 0.0) -> None:
     """out[t, h] = out_scale * softmax_j((q[t, h] . k[j]) * scale + bias[h, distance]) v[j] over the
     keys at positions <= the query's (newer than position - window, if given).  `bias` is float32
-    [heads, distances]; out may be a column view."""
+    [heads, distances] or None; out may be a column view.  With `softcap` > 0 the scaled score (before the
+    bias) becomes softcap * tanh(score / softcap)."""
     _dev(q, out, bias)
     _check(lib().llm_biased_attention(
         q.data_ptr(), out.data_ptr(), dtype_code(q.dtype), out.stride(0), cache.k_ptr, cache.v_ptr,
         cache.block_table.data_ptr(), cache.page_stride, cache.table_stride, cache.page_tokens, cache.kv_heads,
         cache.head_dim, cache.v_dim, _ptr(bias), bias.shape[1] if bias is not None else 0, ctx.positions.data_ptr(),
-        ctx.row_seq.data_ptr(), q_heads, ctx.n_tokens, float(scale), int(window), float(out_scale), ctx.stream),
+        ctx.row_seq.data_ptr(), q_heads, ctx.n_tokens, float(scale), int(window), float(out_scale), float(softcap), ctx.stream),
         "biased_attention")

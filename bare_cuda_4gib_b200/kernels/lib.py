@@ -269,6 +269,7 @@ def swiglu(gate_up: Partials, out: torch.Tensor, n_tokens: int, stream=None) -> 
 
 GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
 CLAMPED_SWISH = "clamped_swish"
+GROUPED_RELU2 = "grouped_relu2"      # the library whose ungated grouped up product stores relu(x)^2
 
 
 def clamped_swish(limit: float, alpha: float) -> str:
@@ -290,6 +291,8 @@ def glu_defines(activation: str):
     constants = clamped_constants(activation)
     if constants is not None:
         return ("-DGLU_CLAMPED", f"-DGLU_LIMIT={constants[0]!r}f", f"-DGLU_ALPHA={constants[1]!r}f")
+    if activation == GROUPED_RELU2:
+        return ("-DGROUPED_UP_RELU2",)
     return {"silu": (), "gelu_tanh": ("-DGLU_GELU_TANH",)}[activation]
 
 

@@ -1,0 +1,53 @@
+"""Launchers of `csrc/mamba2.cu`: the float32 operands of the state scan from a Mamba-2 input
+projection (short convolution, silu, step sizes, decays), and the D term, gate and grouped norm after it."""
+
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build
+from .lib import _check, _dev, dtype_code
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        l = build.load_library("mamba2.cu")
+        P, I, L, F = c_void_p, c_int, c_longlong, c_float
+        l.llm_mamba2_operands.argtypes = [P, I, L, P, P, I, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
+        l.llm_mamba2_finish.argtypes = [P, P, P, P, I, L, P, P, L, I, I, I, I, F, P]
+        for name in ("llm_mamba2_operands", "llm_mamba2_finish"):
+            getattr(l, name).restype = c_int
+        _lib = l
+    return _lib
+
+
+def operands(ctx, u: torch.Tensor, conv_w: torch.Tensor, conv_b: torch.Tensor, ring: torch.Tensor, dt_bias: torch.Tensor,
+             a_log: torch.Tensor, qf, kf, vf, xc, decay, heads: int, vdim: int, state: int, groups: int) -> None:
+    """u [rows, z | x | B | C | dt]: the convolution (history before the step from `ring`) and silu on
+    [x | B | C]; qf, kf [rows, heads * state] = C, B of the head's group; vf [rows, heads * vdim] = dt * x;
+    xc = x; decay [rows, heads] = exp(-exp(a_log) * dt) with dt = softplus(dt + dt_bias).  All float32."""
+    _dev(u, conv_w, conv_b, ring, dt_bias, a_log, qf, kf, vf, xc, decay)
+    for t in (conv_w, conv_b, ring, dt_bias, a_log, qf, kf, vf, xc, decay):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise TypeError("mamba2 operands: constants, ring and operands must be contiguous float32")
+    _check(lib().llm_mamba2_operands(
+        u.data_ptr(), dtype_code(u.dtype), u.stride(0), conv_w.data_ptr(), conv_b.data_ptr(), conv_w.shape[1],
+        ring.data_ptr(), dt_bias.data_ptr(), a_log.data_ptr(), qf.data_ptr(), kf.data_ptr(), vf.data_ptr(), xc.data_ptr(),
+        decay.data_ptr(), ctx.positions.data_ptr(), ctx.row_seq.data_ptr(), ctx.seq_slot.data_ptr(),
+        ctx.seq_q_start.data_ptr(), ctx.n_tokens, heads, vdim, state, groups, ctx.stream), "mamba2_operands")
+
+
+def finish(ctx, scanned: torch.Tensor, xc: torch.Tensor, d_skip: torch.Tensor, z: torch.Tensor, norm_w: torch.Tensor,
+           out: torch.Tensor, vdim: int, parts: int, eps: float) -> None:
+    """out = rms_norm in `parts` equal parts of ((scanned + D x) * silu(z)) * norm_w; z may be a column view."""
+    _dev(scanned, xc, d_skip, z, norm_w, out)
+    if z.dtype != out.dtype or d_skip.dtype != torch.float32 or norm_w.dtype != torch.float32:
+        raise TypeError("mamba2 finish: element types not as the kernel needs")
+    _check(lib().llm_mamba2_finish(scanned.data_ptr(), xc.data_ptr(), d_skip.data_ptr(), z.data_ptr(), dtype_code(z.dtype),
+                                   z.stride(0), norm_w.data_ptr(), out.data_ptr(), out.stride(0), ctx.n_tokens,
+                                   scanned.shape[-1], vdim, parts, float(eps), ctx.stream), "mamba2_finish")

@@ -19,7 +19,7 @@ def lib():
     if _lib is None:
         l = build.load_library("sandwich_norm.cu")
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
-        l.llm_embed_rmsnorm.argtypes = [P, P, P, I, P, I, I, F, P]
+        l.llm_embed_rmsnorm.argtypes = [P, P, P, I, I, P, I, I, F, P]
         l.llm_postnorm_add_rmsnorm.argtypes = [P, P, I, L, P, F, P, F, P, I, P, I, I, P]
         for name in ("llm_embed_rmsnorm", "llm_postnorm_add_rmsnorm"):
             getattr(l, name).restype = c_int
@@ -38,10 +38,10 @@ class NormedDelta:
 
 def embed_rmsnorm(table: torch.Tensor, ids: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, n_tokens: int,
                   eps: float, stream=None) -> None:
-    """out[t] = rms_norm(table[ids[t]]) * weight, float32."""
+    """out[t] = rms_norm(table[ids[t]]) * weight, float32; the weight has the table's type or is float32."""
     _dev(table, ids, weight, out)
     _check(lib().llm_embed_rmsnorm(table.data_ptr(), ids.data_ptr(), weight.data_ptr(), dtype_code(table.dtype),
-                                   out.data_ptr(), n_tokens, table.shape[1], float(eps),
+                                   dtype_code(weight.dtype), out.data_ptr(), n_tokens, table.shape[1], float(eps),
                                    stream if stream is not None else stream_handle()), "embed_rmsnorm")
 
 

@@ -9,8 +9,10 @@ DIFF_ATTENTION_SIZES = ((16, 16), (64, 128), (128, 256))
 def all_libraries():
     jobs = [("plain_kernels.cu", ()), ("gemm_tcgen05.cu", ()), ("gemv_fused.cu", ()), ("stream_kernels.cu", ()),
             ("linear_attention.cu", ()), ("biased_attention.cu", ()), ("sandwich_norm.cu", ()), ("head_prepare.cu", ()),
-            ("latent_attention.cu", ()), ("mlstm.cu", ()), ("diff_attention.cu", ()), ("moe.cu", ())]
-    jobs += [("gemm_tcgen05.cu", ("-DGLU_GELU_TANH",)), ("gemv_fused.cu", ("-DGLU_GELU_TANH",))]
+            ("latent_attention.cu", ()), ("mlstm.cu", ()), ("diff_attention.cu", ()), ("moe.cu", ()),
+            ("gated_sandwich.cu", ()), ("mamba2.cu", ())]
+    jobs += [("gemm_tcgen05.cu", ("-DGLU_GELU_TANH",)), ("gemv_fused.cu", ("-DGLU_GELU_TANH",)),
+             ("gemm_tcgen05.cu", ("-DGROUPED_UP_RELU2",))]
     jobs += [("attention_mma.cu", (f"-DHEAD_DIM={d}",)) for d in ATTENTION_HEAD_DIMS]
     jobs += [("attention_mma.cu", (f"-DHEAD_DIM={d}", "-DDISTANCE_BIAS")) for d in ATTENTION_HEAD_DIMS]
     jobs += [("attention_tcgen05.cu", (f"-DHEAD_DIM={d}",)) for d in (64, 128)]

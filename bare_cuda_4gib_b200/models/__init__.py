@@ -1,3 +1,3 @@
 """Architectures.  Importing this package registers them."""
 
-from . import dopudra, llama, pudulorn, zadurax  # noqa: F401
+from . import dopudra, gurolix, llama, pudulorn, zadurax  # noqa: F401

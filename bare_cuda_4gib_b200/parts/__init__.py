@@ -1,7 +1,7 @@
 """Parts that layers are put together from: mixers, feed-forwards, norms, position encodings,
 block arrangements, embedding and head.  Importing this package registers the built-in parts."""
 
-from . import (attention, biased_attention, block, diff_attention, embedding, latent_attention, linear_attention, mlp,  # noqa: F401
+from . import (attention, biased_attention, block, depth, diff_attention, embedding, latent_attention, linear_attention, mamba2, mlp,  # noqa: F401
                mlstm, moe, norm, parallel, rope, streams)  # (registration)
 from .base import CallContext, KVCacheRequest, Part, StateRequest  # noqa: F401
 from .registry import (build_part, lookup, register_block, register_embedding,  # noqa: F401

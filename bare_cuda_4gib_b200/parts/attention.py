@@ -203,3 +203,114 @@ class GatedAttention(Part):
             K.attention_plain(q, out, call.cache, ctx.positions, ctx.row_seq, self.heads, n, self.scale, window, ctx.stream)
         HP.sigmoid_gate(ctx, out, u[:, u.shape[1] - qd:], n)
         return self.o.forward(ctx, out, n, torch.float32, "attn_proj", allow_partials=True)
+
+
+@register_mixer("general_attention")
+class GeneralAttention(Part):
+    """Grouped-query causal softmax attention with the options several designs combine: biases on the
+    q, k and v projections; an RMS norm per head on q and k (one weight per projection, used as stored)
+    before the rotation; any position part that the norm-and-cache kernel turns (`rotary_halves`,
+    `rotary_pairs`, `none`); a `scale` of its own; a cap on the scaled scores, cap * tanh(score / cap);
+    value heads of their own size; a `window`; and value mixing: with `v_mix` = "source" the values this
+    layer caches are also left for later layers of the step, with "mix" the cached value is (1 - l) v +
+    l v_source of the same token, l the scalar tensor `v_lambda`.
+
+    One product makes [q | k | v]; one kernel adds the biases, norms, turns, mixes and caches; then the
+    engine's tensor-core attention kernels run where they take the shape (equal key and value sizes, no
+    cap), the plain kernel everywhere else.
+
+    params: `hidden`, `heads`, `kv_heads`, `dim`, `vdim`, `scale`, `eps`, `bias` (bool), `qk_norm` (bool),
+    `softcap` (None: no cap), `window` (None: every key), `v_mix` (None | "source" | "mix"), `position`.
+    tensors: `q`, `k`, `v`, `o`, (`q_bias`, `k_bias`, `v_bias`,) (`q_norm`, `k_norm` [dim],) (`v_lambda` [])."""
+
+    takes_lazy_input = False
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        p = self.params
+        self.hidden, self.heads, self.kv_heads = int(p["hidden"]), int(p["heads"]), int(p["kv_heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p.get("vdim") or p["dim"])
+        if self.heads % self.kv_heads:
+            raise ConfigError(f"general_attention: {self.heads} heads cannot share {self.kv_heads} key/value heads")
+        if self.vdim > 256:
+            raise ConfigError(f"general_attention: value head size {self.vdim} exceeds the 256 the kernels take")
+        self.window = p.get("window")
+        self.has_bias, self.qk_norm = bool(p.get("bias")), bool(p.get("qk_norm"))
+        self.softcap = float(p["softcap"]) if p.get("softcap") else 0.0
+        self.v_mix = p.get("v_mix")
+        if self.v_mix not in (None, "source", "mix"):
+            raise ConfigError(f"general_attention: v_mix must be None, 'source' or 'mix', got {self.v_mix!r}")
+        self.position = build_part("position", p["position"])
+        self.scale = float(p.get("scale") or 1.0 / math.sqrt(self.dim))
+        self.eps = float(p.get("eps", 1e-6))
+        self.qd, self.kd, self.vd = self.heads * self.dim, self.kv_heads * self.dim, self.kv_heads * self.vdim
+
+    def children(self):
+        return [self.position]
+
+    def local_weights(self):
+        out = {"q": ((self.qd, self.hidden), "matrix"), "k": ((self.kd, self.hidden), "matrix"),
+               "v": ((self.vd, self.hidden), "matrix"), "o": ((self.hidden, self.heads * self.vdim), "matrix")}
+        if self.has_bias:
+            out.update({"q_bias": ((self.qd,), "zero"), "k_bias": ((self.kd,), "zero"), "v_bias": ((self.vd,), "zero")})
+        if self.qk_norm:
+            out.update({"q_norm": ((self.dim,), "norm"), "k_norm": ((self.dim,), "norm")})
+        if self.v_mix is not None:
+            out["v_lambda"] = ((), "zero")      # the source layer has the tensor too and does not use it
+        return out
+
+    def adjacent_weights(self):
+        return [("q", "k", "v")]
+
+    def cache_request(self):
+        return KVCacheRequest(self.kv_heads, self.dim, self.window, None if self.vdim == self.dim else self.vdim)
+
+    def state_request(self):
+        return None
+
+    def prepare(self, dtype, device) -> None:
+        t = self.tensors
+        self.proj = Linear(fused_rows([t["q"], t["k"], t["v"]]), "general_attention.in")
+        self.o = Linear(t["o"], "general_attention.o")
+        self.proj.prepare(dtype)
+        self.o.prepare(dtype)
+        self.bias = (torch.cat([t[n].to(torch.float32).reshape(-1) for n in ("q_bias", "k_bias", "v_bias")]).contiguous()
+                     if self.has_bias else None)
+        self.q_norm = t["q_norm"].to(dtype).contiguous() if self.qk_norm else None
+        self.k_norm = t["k_norm"].to(dtype).contiguous() if self.qk_norm else None
+        self.v_lambda = float(t["v_lambda"].to(torch.float32).reshape(-1)[0].item()) if self.v_mix == "mix" else 0.0
+        self.position.prepare(dtype, device)
+        self.inv_freq = getattr(self.position, "inv_freq", None)
+        self.rot_dims = int(getattr(self.position, "dims", 0)) if self.inv_freq is not None else 0
+        if self.rot_dims > self.dim:
+            raise ConfigError(f"general_attention: {self.rot_dims} rotated entries in a head of {self.dim}")
+        self.halves = bool(getattr(self.position, "halves", False))
+        self.magnitude = float(getattr(self.position, "magnitude", 1.0))
+        self.fast = None
+        if dtype == torch.bfloat16 and device.type == "cuda" and self.vdim == self.dim and not self.softcap:
+            from ..kernels import attention as fast
+            self.fast = fast.plan_for(self.dim, self.heads, self.kv_heads)
+
+    def plan_step(self, ctx) -> None:
+        if self.fast is not None and ctx.use_fast_attention:
+            from ..kernels import attention as fast
+            fast.step_tiles(ctx, self.fast)
+
+    def forward(self, ctx, call, h):
+        from ..kernels import biased_attention as BA, head_prepare as HP
+        n = ctx.n_tokens
+        u = self.proj.forward(ctx, h, n, ctx.dtype, "mixer_in").tensor
+        q = ctx.ws.get("q", (n, self.qd), ctx.dtype)
+        shared = ctx.ws.get("mixed_values", (n, self.vd), torch.float32) if self.v_mix else None
+        HP.headnorm_rope_cache(ctx, u, 0, self.qd, self.qd + self.kd, self.q_norm, self.k_norm, self.eps, self.inv_freq,
+                               self.rot_dims, self.magnitude, q, call.cache, self.heads, call.writes_cache,
+                               halves=self.halves, bias=self.bias, v_mix_in=shared if self.v_mix == "mix" else None,
+                               v_mix=self.v_lambda, v_mix_out=shared if self.v_mix == "source" else None)
+        out = ctx.ws.get("attn_out", (n, self.heads * self.vdim), ctx.dtype)
+        window = int(self.window) if self.window else 0
+        if self.fast is not None and ctx.use_fast_attention:
+            from ..kernels import attention as fast
+            fast.run(ctx, self.fast, q, out, call.cache, self.scale, window)
+        else:
+            BA.attention(ctx, q, out, call.cache, None, self.heads, self.scale, window, 1.0, self.softcap)
+        return self.o.forward(ctx, out, n, torch.float32, "attn_proj", allow_partials=True)

@@ -73,16 +73,21 @@ class ScaledPositionEmbedding(Part):
 
 @register_embedding("table_norm")
 class NormedEmbedding(Part):
-    """x = rms_norm(E[id]) * w, in float32.
+    """x = rms_norm(E[id]) * w, in float32; with `one_plus` the weight is stored around zero and the
+    factor is 1 + w, formed once in float32.
 
-    params: `vocab`, `hidden`, `eps`.  tensors: `weight` [vocab, hidden], `norm` [hidden]."""
+    params: `vocab`, `hidden`, `eps`, `one_plus` (optional).  tensors: `weight` [vocab, hidden], `norm` [hidden]."""
 
     def local_weights(self):
         p = self.params
-        return {"weight": ((int(p["vocab"]), int(p["hidden"])), "matrix"), "norm": ((int(p["hidden"]),), "norm")}
+        return {"weight": ((int(p["vocab"]), int(p["hidden"])), "matrix"),
+                "norm": ((int(p["hidden"]),), "zero" if p.get("one_plus") else "norm")}
 
     def prepare(self, dtype, device) -> None:
-        self.norm = self.tensors["norm"].to(self.tensors["weight"].dtype).contiguous()
+        if self.params.get("one_plus"):
+            self.norm = (1.0 + self.tensors["norm"].to(torch.float32)).contiguous()
+        else:
+            self.norm = self.tensors["norm"].to(self.tensors["weight"].dtype).contiguous()
 
     def forward(self, ctx) -> torch.Tensor:
         from ..kernels import sandwich as SW

@@ -14,9 +14,22 @@ run them in plain arithmetic.  A row of a product depends on that row alone, and
 in the order of the choice, so a token's result does not depend on what else is in the step.  The
 shared expert runs on the engine's dense products.
 
+Options beside that form (each off unless its parameter is given):
+
+* `expert_form` "relu2": an expert is W_down relu(W_up h)^2, with no gate matrix;
+* `identity` n: the router has n more outputs behind the experts' own, identity experts without tensors
+  whose result is h itself (times the weight);
+* `correction`: a tensor with one number per router output that is added to the score for the choice
+  only; the weight stays the score;
+* `groups`, `keep`: the router's outputs (identity experts included) form `groups` equal groups of
+  neighbours, a group counts by its largest choice value, and only experts of the `keep` best groups can
+  be chosen.
+
 params: `hidden`, `experts`, `top`, `router_scale`, `intermediate`, `shared_intermediate` (None: no shared
-expert), `shared_gate` (bool).  tensors: `router` [experts, hidden], `e<j>.gate|up` [intermediate, hidden],
-`e<j>.down` [hidden, intermediate], `shared.gate|up|down`, `shared.sg` [1, hidden].
+expert), `shared_gate` (bool), `expert_form`, `identity`, `correction` (bool), `groups`, `keep`.
+tensors: `router` [experts + identity, hidden], `correction` [experts + identity], `e<j>.gate|up`
+[intermediate, hidden] (relu2: `e<j>.up` only), `e<j>.down` [hidden, intermediate], `shared.gate|up|down`,
+`shared.sg` [1, hidden].
 """
 
 from __future__ import annotations
@@ -42,15 +55,31 @@ class MixtureOfExperts(Part):
         self.router_scale = float(p.get("router_scale", 1.0))
         self.shared_ff = int(p["shared_intermediate"]) if p.get("shared_intermediate") else 0
         self.has_shared_gate = bool(p.get("shared_gate")) and self.shared_ff > 0
+        self.gated = p.get("expert_form", "glu_silu") != "relu2"
+        if p.get("expert_form", "glu_silu") not in ("glu_silu", "relu2"):
+            raise ConfigError(f"moe: expert_form '{p.get('expert_form')}' is not one of ['glu_silu', 'relu2']")
+        self.identity = int(p.get("identity") or 0)
+        self.outputs = self.experts + self.identity          # what the router scores
+        self.has_correction = bool(p.get("correction"))
+        self.groups, self.keep = int(p.get("groups") or 1), int(p.get("keep") or p.get("groups") or 1)
         from ..kernels.moe import MAX_EXPERTS
-        if not (1 <= self.top <= self.experts <= MAX_EXPERTS):
-            raise ConfigError(f"moe: {self.top} of {self.experts} experts (at most {MAX_EXPERTS}) cannot be chosen")
+        if not (1 <= self.top <= self.outputs <= MAX_EXPERTS) or self.experts < 1:
+            raise ConfigError(f"moe: {self.top} of {self.outputs} experts (at most {MAX_EXPERTS}) cannot be chosen")
+        if self.groups > 1 and (self.outputs % self.groups or not (1 <= self.keep <= self.groups)
+                                or self.top > self.keep * (self.outputs // self.groups)):
+            raise ConfigError(f"moe: {self.outputs} router outputs in {self.groups} groups of which {self.keep} stay "
+                              f"cannot give {self.top} choices")
+
+    def _matrices(self):
+        return ("gate", "up") if self.gated else ("up",)
 
     def local_weights(self):
-        out = {"router": ((self.experts, self.hidden), "matrix")}
+        out = {"router": ((self.outputs, self.hidden), "matrix")}
+        if self.has_correction:
+            out["correction"] = ((self.outputs,), "zero")
         for e in range(self.experts):
-            out[f"e{e}.gate"] = ((self.ff, self.hidden), "matrix")
-            out[f"e{e}.up"] = ((self.ff, self.hidden), "matrix")
+            for n in self._matrices():
+                out[f"e{e}.{n}"] = ((self.ff, self.hidden), "matrix")
             out[f"e{e}.down"] = ((self.hidden, self.ff), "matrix")
         if self.shared_ff:
             out["shared.gate"] = ((self.shared_ff, self.hidden), "matrix")
@@ -61,7 +90,7 @@ class MixtureOfExperts(Part):
         return out
 
     def adjacent_weights(self):
-        groups = [tuple(f"e{e}.{t}" for e in range(self.experts) for t in ("gate", "up")),
+        groups = [tuple(f"e{e}.{t}" for e in range(self.experts) for t in self._matrices()),
                   tuple(f"e{e}.down" for e in range(self.experts))]
         if self.shared_ff:
             groups.append(("shared.gate", "shared.up"))
@@ -70,7 +99,8 @@ class MixtureOfExperts(Part):
     def prepare(self, dtype, device) -> None:
         t = self.tensors
         E = self.experts
-        self.w_up = fused_rows([t[f"e{e}.{n}"] for e in range(E) for n in ("gate", "up")]).to(dtype).contiguous()
+        self.w_up = fused_rows([t[f"e{e}.{n}"] for e in range(E) for n in self._matrices()]).to(dtype).contiguous()
+        self.correction = t["correction"].to(torch.float32).contiguous() if self.has_correction else None
         self.w_down = fused_rows([t[f"e{e}.down"] for e in range(E)]).to(dtype).contiguous()
         self.w_router = t["router"].contiguous()
         self.w_sg = t["shared.sg"].to(self.w_router.dtype).reshape(-1).contiguous() if self.has_shared_gate else None
@@ -81,10 +111,10 @@ class MixtureOfExperts(Part):
             self.shared_down.prepare(dtype)
         from ..kernels.moe import GroupedPlan
         # bfloat16 experts whose rows the copy engine can fetch run on the tensor cores
-        self.plan = (GroupedPlan(self.w_up, self.w_down, E)
+        self.plan = (GroupedPlan(self.w_up, self.w_down, E, self.gated)
                      if self.w_up.is_cuda and self.ff % 8 == 0 and GroupedPlan.takes(self.w_up, self.w_down) else None)
         for e in range(E):      # the stacked matrices stand for them from here on
-            for n in ("gate", "up", "down"):
+            for n in self._matrices() + ("down",):
                 t.pop(f"e{e}.{n}")
         t["experts.up"], t["experts.down"] = self.w_up, self.w_down
 
@@ -101,7 +131,8 @@ class MixtureOfExperts(Part):
         tiles = ctx.ws.get("moe_tiles", (n, 3 * (top + E) + 1), i32)
         tc = self.plan is not None and ctx.dtype == torch.bfloat16 and h.dtype == torch.bfloat16
         n_tiles = tiles.view(-1)[3 * M.max_tiles(slots, E, tc):]
-        M.route(ctx, h, self.w_router, self.w_sg, top, self.router_scale, ids, weights, gate, n)
+        M.route(ctx, h, self.w_router, self.w_sg, top, self.router_scale, ids, weights, gate, n, self.correction,
+                self.groups, self.keep)
         M.sort(ctx, ids, slots, E, sorted_slots, tiles, n_tiles, tc)
         act = ctx.ws.get("moe_act", (n, top * self.ff), ctx.dtype)
         act_rows = act.view(-1)[: slots * self.ff].view(slots, self.ff)
@@ -116,7 +147,7 @@ class MixtureOfExperts(Part):
                              sorted_slots, tiles, n_tiles, weights, slots)
         else:
             M.grouped(ctx, h, self.w_up, act, False, sorted_slots, tiles, n_tiles, weights, top, self.ff, self.hidden,
-                      slots, E)
+                      slots, E, self.gated)
             M.grouped(ctx, act_rows, self.w_down, y, True, sorted_slots, tiles, n_tiles, weights, top, self.hidden, self.ff,
                       slots, E)
         shared = None
@@ -124,5 +155,8 @@ class MixtureOfExperts(Part):
             a = self.shared_gate_up.forward(ctx, h, n, ctx.dtype, "moe_shared_act", glu="silu")
             shared = self.shared_down.forward(ctx, a.tensor, n, f32, "moe_shared_out", allow_partials=True)
         out = ctx.ws.get("ffn_out", (n, self.hidden), f32)
-        M.combine(ctx, y, top, shared, gate, out, n, self.hidden)
+        if self.identity:
+            M.combine(ctx, y, top, shared, gate, out, n, self.hidden, ids, weights, E, h)
+        else:
+            M.combine(ctx, y, top, shared, gate, out, n, self.hidden)
         return K.Partials(out)

@@ -83,3 +83,29 @@ class SandwichRMSNorm(Part):
         out = ctx.ws.get(buffer, (rows, self.params["size"]), ctx.dtype)
         SW.postnorm_add_rmsnorm(residual, delta, self.weight, out, float(self.params["eps"]), rows, row_index, ctx.stream)
         return out
+
+
+@register_norm("gated_sandwich_rmsnorm")
+class GatedSandwichRMSNorm(Part):
+    """RMS norm of a stream whose sublayers are normed on both sides and gated, x <- x + norm_b(gate *
+    f(norm(x))), with float32 factors.  As the norm before a sublayer it first does what is pending (a
+    `kernels.gated_sandwich.GatedDelta`: gate, norm behind the sublayer, add, and at a layer's end the
+    weighted sum over the layers so far), in the same kernel; as the norm behind a sublayer it only
+    lends its factor (`factor`).
+
+    params: `size`, `eps`, `one_plus` (the weight is stored around zero and the factor is 1 + w).
+    tensors: `weight` [size]."""
+
+    def local_weights(self):
+        return {"weight": ((self.params["size"],), "zero" if self.params.get("one_plus") else "norm")}
+
+    def prepare(self, dtype, device) -> None:
+        w = self.tensors["weight"].to(torch.float32)
+        self.factor = ((1.0 + w) if self.params.get("one_plus") else w).contiguous()
+
+    def forward(self, ctx, residual: torch.Tensor, delta, rows: int, row_index: Optional[torch.Tensor] = None,
+                buffer: str = "normed", lazy: bool = False):
+        from ..kernels import gated_sandwich as GS
+        out = ctx.ws.get(buffer, (rows, self.params["size"]), ctx.dtype)
+        GS.step(residual, delta, self.factor, out, float(self.params["eps"]), rows, row_index, ctx.stream)
+        return out

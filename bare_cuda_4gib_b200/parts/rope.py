@@ -84,17 +84,31 @@ class HalvesRotaryPositions(Part):
     entry i + dims / 2 (the rest pass) by the angle position * f_i, f_i = base^(-2i / dims): the pair
     (u, v) becomes (u cos - v sin, v cos + u sin).
 
+    With `scaling` {factor, low, high, original} (the rule of Llama 3.1, by wavelength l = 2 pi / f): a
+    frequency with l < original / high stays, one with l > original / low becomes f / factor, and in
+    between, with s = (original / l - low) / (high - low), it becomes (1 - s) f / factor + s f.
+
     The kernels that norm and cache q and k turn them with `inv_freq` themselves (`halves` tells them
-    the pairing).  params: `dims`, `base`.  No tensors."""
+    the pairing).  params: `dims`, `base`, `scaling` (or None).  No tensors."""
 
     halves = True
     magnitude = 1.0
 
     def prepare(self, dtype, device) -> None:
+        import math
+
         dims, base = int(self.params["dims"]), float(self.params["base"])
         self.dims = dims
         i = torch.arange(dims // 2, dtype=torch.float64)
-        self.inv_freq = (base ** (-2.0 * i / dims)).to(torch.float32).to(device)
+        f = base ** (-2.0 * i / dims)
+        sc = self.params.get("scaling")
+        if sc:
+            factor, low, high, original = (float(sc[k]) for k in ("factor", "low", "high", "original"))
+            length = 2.0 * math.pi / f
+            s = ((original / length - low) / (high - low)).clamp(0.0, 1.0) if high != low else torch.ones_like(f)
+            blended = (1.0 - s) * f / factor + s * f
+            f = torch.where(length < original / high, f, torch.where(length > original / low, f / factor, blended))
+        self.inv_freq = f.to(torch.float32).to(device)
 
     def fused_rotation(self):
         return None      # the fused attention kernels turn whole heads; this one may turn a head's first entries only
