@@ -105,6 +105,31 @@ PRESETS.update({
 })
 
 
+def _gurolix(width, vocab, blocks, heads, kv_heads, dim, vdim, state_heads, state_vdim, state, state_groups, experts, top,
+             identity, groups, ff):
+    """`blocks` times: capped attention, Mamba-2, normed attention, Mamba-2, each with a mixture of experts."""
+    mlp = {"kind": "moe", "expert": {"ff": ff},
+           "router": {"experts": experts, "top": top, "identity": identity, "groups": {"count": groups[0], "keep": groups[1]}}}
+    common = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "v_mix": True}
+    capped = {"type": "attention_2", "mlp": mlp,
+              "mixer": dict(common, softcap=30.0, rot={"base": 500000.0, "dims": dim, "scaling": {
+                  "factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})}
+    normed = {"type": "attention", "mlp": mlp, "mixer": dict(common, rot={"base": 10000.0, "dims": dim // 2})}
+    ssm = {"type": "mamba2", "mlp": mlp,
+           "mixer": {"heads": state_heads, "vdim": state_vdim, "state": state, "groups": state_groups, "conv": 4,
+                     "norm_groups": state_groups}}
+    return dict(architecture="Gurolix", vocab=vocab, width=width, norm={"eps": 1e-5}, layers=[capped, ssm, normed, ssm] * blocks)
+
+
+PRESETS.update({
+    "gurolix-tiny": _gurolix(64, 300, 1, 4, 2, 16, 8, 4, 8, 16, 2, 5, 2, 1, (3, 2), 32),
+    # widths and expert sizes of the Pudulorn presets; attention heads of 128 with values of 64 (of 128 at the larger
+    # size), Mamba-2 with twice the width inside, heads of 64 and states of 128
+    "gurolix-2048": _gurolix(2048, 32000, 1, 16, 4, 128, 64, 64, 64, 128, 8, 8, 2, 2, (5, 3), 1408),
+    "gurolix-4096": _gurolix(4096, 32000, 1, 32, 8, 128, 128, 128, 64, 128, 8, 8, 2, 2, (5, 3), 2752),
+})
+
+
 def preset_config(name: str, **overrides):
     from ..config.llama import LlamaConfig
     from ..errors import ConfigError

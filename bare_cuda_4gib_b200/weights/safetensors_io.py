@@ -129,7 +129,7 @@ def write_safetensors(path, tensors: Dict[str, torch.Tensor]) -> None:
         t = tensors[name].detach().cpu().contiguous()
         if t.dtype not in _NAMES:
             raise WeightError(f"cannot write tensor '{name}' of dtype {t.dtype}")
-        raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""      # (a scalar has no axis to view)
         header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [offset, offset + len(raw)]}
         offset += len(raw)
         blobs.append(raw)

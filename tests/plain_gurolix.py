@@ -142,19 +142,29 @@ def mamba2(t: Dict[str, torch.Tensor], p: str, m, h, eps):
     return y @ t[p + "o"].T
 
 
-def route(t: Dict[str, torch.Tensor], p: str, r, h):
-    """Returns (ids [n, top], weights [n, top]); ids from `experts` on are identity experts."""
+def route(t: Dict[str, torch.Tensor], p: str, r, h, margins: Optional[list] = None):
+    """Returns (ids [n, top], weights [n, top]); ids from `experts` on are identity experts.  `margins`
+    receives, per token, how far the last group kept lies above the first one barred, and the last expert
+    chosen above the first one left out (infinite where there is no such pair)."""
     z = h @ t[p + "router"].T
     s = torch.softmax(z, -1)
     choice = s + t[p + "correction"]
-    total = r["experts"] + r.get("identity", 0)
-    count, keep = r["groups"]["count"], r["groups"]["keep"]
+    total = r["experts"] + (r.get("identity") or 0)
+    groups = r.get("groups") or {"count": 1, "keep": 1}
+    count, keep = groups["count"], groups["keep"]
     best = choice.view(-1, count, total // count).max(-1).values
+    ranked = best.sort(-1, descending=True).values
     kept = torch.zeros_like(best, dtype=torch.bool)
     kept.scatter_(1, best.topk(keep, -1).indices, True)
     allowed = kept[:, :, None].expand(-1, -1, total // count).reshape(-1, total)
     choice = choice.masked_fill(~allowed, -math.inf)
     ids = choice.topk(r["top"], -1).indices
+    if margins is not None:
+        inf = torch.full((h.shape[0],), math.inf, dtype=F64)
+        order = choice.sort(-1, descending=True).values
+        margins.append(ranked[:, keep - 1] - ranked[:, keep] if keep < count else inf)
+        margins.append(torch.nan_to_num(order[:, r["top"] - 1] - order[:, r["top"]], nan=math.inf, posinf=math.inf)
+                       if r["top"] < total else inf)
     return ids, s.gather(1, ids)
 
 
@@ -162,9 +172,9 @@ def expert(t, p: str, e: int, h):
     return torch.relu(h @ t[f"{p}e{e}.up"].T) ** 2 @ t[f"{p}e{e}.down"].T
 
 
-def mixture(t: Dict[str, torch.Tensor], p: str, mlp, h):
+def mixture(t: Dict[str, torch.Tensor], p: str, mlp, h, margins: Optional[list] = None):
     r = mlp["router"]
-    ids, weights = route(t, p, r, h)
+    ids, weights = route(t, p, r, h, margins)
     out = torch.zeros_like(h)
     for i in range(h.shape[0]):
         for e, w in zip(ids[i].tolist(), weights[i]):
@@ -176,8 +186,10 @@ def residual_gate(t, name: str, h):
     return torch.sigmoid(h @ t[name].T + t[name + ".b"])
 
 
-def forward(config, tensors: Dict[str, torch.Tensor], tokens: List[int], collect: Optional[list] = None):
-    """Logits [n, vocab] of one sequence; `collect` receives the stream after every layer."""
+def forward(config, tensors: Dict[str, torch.Tensor], tokens: List[int], collect: Optional[list] = None,
+            margins: Optional[list] = None):
+    """Logits [n, vocab] of one sequence; `collect` receives the stream after every layer, `margins` the
+    routers' margins (see `route`)."""
     t = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in tensors.items()}
     eps = config["norm"]["eps"]
     x = norm_around_zero(t["embed"][torch.tensor(tokens)], t["embed.norm"], eps)
@@ -198,7 +210,7 @@ def forward(config, tensors: Dict[str, torch.Tensor], tokens: List[int], collect
         x = x + norm_around_zero(y * residual_gate(t, name + "rg1", h), t[name + "norm1b"], eps)
         if layer.get("mlp") is not None:
             h = norm_around_zero(x, t[name + "norm2"], eps)
-            y = mixture(t, name + "mlp.", layer["mlp"], h)
+            y = mixture(t, name + "mlp.", layer["mlp"], h, margins)
             x = x + norm_around_zero(y * residual_gate(t, name + "rg2", h), t[name + "norm2b"], eps)
         history.append(x)
         w = t[name + "dwa"]
