@@ -66,6 +66,28 @@ CFG_A, CFG_B = _cfg_a(), _cfg_b()
 CONFIGS = {"A": (CFG_A, 16), "B": (CFG_B, 32)}
 
 
+def every_expert_chosen(cfg):
+    """The same model with routers that choose every expert (identity experts included) and bar no group.
+    A router's choice is a discontinuity: where two choice values nearly tie, the rounding of a bfloat16
+    run picks the other expert and the row moves by a whole expert's result, which says nothing about the
+    kernels.  bfloat16 runs are therefore compared on this variant, whose logits are continuous in every
+    rounding error, with the same tensors; the choice itself is compared in float32, where a tie within
+    rounding is rare enough to be drawn around (`clear_ids`)."""
+    import copy
+    out = copy.deepcopy(cfg)
+    for layer in out["layers"]:
+        if layer.get("mlp") is not None:
+            r = layer["mlp"]["router"]
+            r["top"] = r["experts"] + (r.get("identity") or 0)
+            r.pop("groups", None)
+    return out
+
+
+def config_for(name: str, dtype: str):
+    cfg, page = CONFIGS[name]
+    return (every_expert_chosen(cfg) if dtype == "bfloat16" else cfg), page
+
+
 def tensor_shapes(cfg) -> Dict[str, Tuple[int, ...]]:
     W = cfg["width"]
     out = {"embed": (cfg["vocab"], W), "embed.norm": (W,), "final.norm": (W,), "head": (cfg["vocab"], W)}
@@ -145,10 +167,11 @@ _tensors: Dict[str, Dict[str, torch.Tensor]] = {}
 
 
 @functools.lru_cache(maxsize=None)
-def model_folder(name: str, seed: int = 3):
-    cfg, _page = CONFIGS[name]
-    folder = H.tmp_root() / f"gurolix{name}-{seed}"
-    register(folder, cfg, random_tensors(cfg, seed))
+def model_folder(name: str, seed: int = 3, dtype: str = "float32"):
+    """The folder of configuration `name`; for bfloat16 runs the variant whose routers choose every expert."""
+    cfg, _page = config_for(name, dtype)
+    folder = H.tmp_root() / f"gurolix{name}-{seed}-{dtype}"
+    register(folder, cfg, random_tensors(CONFIGS[name][0], seed))
     return folder
 
 
