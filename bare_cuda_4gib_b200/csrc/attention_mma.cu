@@ -30,6 +30,10 @@
 // as a sum of two bfloat16 numbers (the weight rounded, and what the rounding left), so a weight
 // keeps 16 significant bits instead of 8.  The output may be a column view of a wider matrix
 // (`out_stride`) and is multiplied by `out_scale`.
+//
+// -DV_DIM=n builds the kernel for value heads of n entries beside key heads of HEAD_DIM (a multiple of 16 up
+// to 128; default: HEAD_DIM).  -DSCORE_CAP builds the variant whose scaled score s becomes cap * tanh(s / cap)
+// before the softmax (entry point `llm_attention_mma_general`, which every build has for its value size).
 
 #include "common.cuh"
 
@@ -39,11 +43,18 @@
 
 namespace {
 
+#ifndef V_DIM
+#define V_DIM HEAD_DIM
+#endif
 constexpr int D = HEAD_DIM;
+constexpr int DV = V_DIM;     // entries of a value head
 static_assert(D % 16 == 0 && D >= 16 && D <= 128, "HEAD_DIM must be a multiple of 16 up to 128");
+static_assert(DV % 16 == 0 && DV >= 16 && DV <= 128, "V_DIM must be a multiple of 16 up to 128");
 constexpr int BN = 64;        // keys per block
 constexpr int LDS = D + 8;    // padded row length in shared memory (conflict-free ldmatrix)
 constexpr int CHUNKS = D / 8; // 16-byte chunks per row
+constexpr int LDSV = DV + 8;  // the same for value rows
+constexpr int CHUNKS_V = DV / 8;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -90,7 +101,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 struct AttnArgs {
   const __nv_bfloat16* q;      // [tokens, q_heads, D]
-  __nv_bfloat16* out;          // [tokens, q_heads * D]
+  __nv_bfloat16* out;          // [tokens, q_heads * DV]
   PagedCache cache;
   const int32_t* seq_q_start;  // per batch sequence: first row of its tokens in this step
   const int32_t* seq_q_len;    // tokens it brings
@@ -107,7 +118,16 @@ struct AttnArgs {
   float out_scale;             // factor on the output
   const float* bias;           // DISTANCE_BIAS: [q_heads][bias_len] by distance
   int bias_len;
+  float scale_over_cap;        // SCORE_CAP: scale / cap, and cap * log2(e)
+  float cap_log2;
 };
+
+// SCORE_CAP: what a raw score q . k becomes, in base-2 units: cap * tanh(score * scale / cap) * log2(e), with
+// tanh(x) = 1 - 2 / (e^(2x) + 1) from the hardware's 2^x (absolute error near 1e-7).
+__device__ __forceinline__ float capped_score(float raw, float scale_over_cap, float cap_log2) {
+  const float t = fast_exp2(raw * scale_over_cap * 2.8853900817779268f);
+  return cap_log2 * (1.0f - __fdividef(2.0f, t + 1.0f));
+}
 
 template <int WARPS_M, int WARPS_N, int MT>
 __global__ void __launch_bounds__(WARPS_M* WARPS_N * 32)
@@ -124,7 +144,7 @@ attention_mma_kernel(AttnArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);      // [BM][LDS]
   __nv_bfloat16* Ks = Qs + BM * LDS;                                   // [STAGES][BN][LDS]
-  __nv_bfloat16* Vs = Ks + STAGES * BN * LDS;                          // [STAGES][BN][LDS]
+  __nv_bfloat16* Vs = Ks + STAGES * BN * LDS;                          // [STAGES][BN][LDSV]
 
   pdl_launch_dependents();
   pdl_wait();
@@ -178,17 +198,22 @@ attention_mma_kernel(AttnArgs a) {
   const bool block_in_page = (page_tokens % BN) == 0;
   const int32_t* table_row = a.cache.block_table + (long long)seq * a.cache.table_stride;
   const long long head_offset = (long long)kvh * page_tokens * D;
+  const long long head_offset_v = (long long)kvh * page_tokens * DV;
   constexpr int LOADS = (BN * CHUNKS + NT_THREADS - 1) / NT_THREADS;   // 16-byte chunks per thread and block
+  constexpr int LOADS_V = (BN * CHUNKS_V + NT_THREADS - 1) / NT_THREADS;
   // copies block kb into its stage (nothing if kb is past the end) and closes one cp.async group
   auto load_block = [&](int kb, int stage) {
     if (kb < kb_end) {
       __nv_bfloat16* ks = Ks + stage * BN * LDS;
-      __nv_bfloat16* vs = Vs + stage * BN * LDS;
+      __nv_bfloat16* vs = Vs + stage * BN * LDSV;
       const int key0 = kb * BN;
-      long long block_base = -1;
+      long long block_base = -1, block_base_v = -1;
       if (block_in_page) {
         const int page = __ldg(table_row + key0 / page_tokens);
-        if (page >= 0) block_base = (long long)page * a.cache.page_stride + head_offset + (long long)(key0 % page_tokens) * D;
+        if (page >= 0) {
+          block_base = (long long)page * a.cache.page_stride + head_offset + (long long)(key0 % page_tokens) * D;
+          block_base_v = (long long)page * a.cache.page_stride + head_offset_v + (long long)(key0 % page_tokens) * DV;
+        }
       }
 #pragma unroll
       for (int j = 0; j < LOADS; ++j) {
@@ -207,7 +232,27 @@ attention_mma_kernel(AttnArgs a) {
           if (valid) src = (long long)page * a.cache.page_stride + head_offset + (long long)(key % page_tokens) * D + c * 8;
         }
         cp_async16(ks + r * LDS + c * 8, kc + src, valid);
-        cp_async16(vs + r * LDS + c * 8, vc + src, valid);
+        if (D == DV) cp_async16(vs + r * LDSV + c * 8, vc + src, valid);
+      }
+      if (D != DV) {
+#pragma unroll
+        for (int j = 0; j < LOADS_V; ++j) {
+          const int i = threadIdx.x + j * NT_THREADS;
+          if (BN * CHUNKS_V % NT_THREADS != 0 && i >= BN * CHUNKS_V) break;
+          const int r = i / CHUNKS_V, c = i % CHUNKS_V;
+          long long src = 0;
+          bool valid = key0 + r < kv_len;
+          if (block_in_page) {
+            valid = valid && block_base_v >= 0;
+            if (valid) src = block_base_v + r * DV + c * 8;
+          } else if (valid) {
+            const int key = key0 + r;
+            const int page = __ldg(table_row + key / page_tokens);
+            valid = page >= 0;
+            if (valid) src = (long long)page * a.cache.page_stride + head_offset_v + (long long)(key % page_tokens) * DV + c * 8;
+          }
+          cp_async16(vs + r * LDSV + c * 8, vc + src, valid);
+        }
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -231,7 +276,7 @@ attention_mma_kernel(AttnArgs a) {
   const float* row_bias[MT][2];  // the bias row of this row's head
 #endif
   float m[MT][2], l[MT][2];
-  float o[MT][D / 8][4];
+  float o[MT][DV / 8][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
@@ -245,7 +290,7 @@ attention_mma_kernel(AttnArgs a) {
       l[mt][h] = 0.0f;
     }
 #pragma unroll
-    for (int i = 0; i < D / 8; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.0f;
+    for (int i = 0; i < DV / 8; ++i) o[mt][i][0] = o[mt][i][1] = o[mt][i][2] = o[mt][i][3] = 0.0f;
   }
 
   for (int kb = kb_begin; kb < kb_end; ++kb) {
@@ -254,7 +299,7 @@ attention_mma_kernel(AttnArgs a) {
     __syncthreads();  // block kb has landed; everyone is done with the stage used one block ago
     load_block(kb + STAGES - 1, (kb - kb_begin + STAGES - 1) % STAGES);
     const __nv_bfloat16* ks_ = Ks + stage * BN * LDS;
-    const __nv_bfloat16* vs_ = Vs + stage * BN * LDS;
+    const __nv_bfloat16* vs_ = Vs + stage * BN * LDSV;
     const int key0 = kb * BN + wn * KEYS_W;  // first key this warp scores
 
     float s[MT][NT][4];
@@ -294,7 +339,11 @@ attention_mma_kernel(AttnArgs a) {
         for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
+#ifdef SCORE_CAP
+            const float v = capped_score(s[mt][nt][e], a.scale_over_cap, a.cap_log2);
+#else
             const float v = s[mt][nt][e] * a.scale_log2;
+#endif
             s[mt][nt][e] = v;
             mx[e >> 1] = fmaxf(mx[e >> 1], v);
           }
@@ -311,6 +360,8 @@ attention_mma_kernel(AttnArgs a) {
             const float v = visible ? fmaf(s[mt][nt][e], a.scale_log2,
                                            1.4426950408889634f * __ldg(row_bias[mt][h] + min(row_pos[mt][h] - key, a.bias_len - 1)))
                                     : -INFINITY;
+#elif defined(SCORE_CAP)
+            const float v = visible ? capped_score(s[mt][nt][e], a.scale_over_cap, a.cap_log2) : -INFINITY;
 #else
             const float v = visible ? s[mt][nt][e] * a.scale_log2 : -INFINITY;
 #endif
@@ -333,7 +384,7 @@ attention_mma_kernel(AttnArgs a) {
       // most blocks leave every row's maximum where it was: nothing to rescale then
       if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
 #pragma unroll
-        for (int i = 0; i < D / 8; ++i) {
+        for (int i = 0; i < DV / 8; ++i) {
           o[mt][i][0] *= corr[0];
           o[mt][i][1] *= corr[0];
           o[mt][i][2] *= corr[1];
@@ -361,10 +412,10 @@ attention_mma_kernel(AttnArgs a) {
 #pragma unroll
     for (int kk = 0; kk < KEYS_W / 16; ++kk) {
 #pragma unroll
-      for (int dt = 0; dt < D / 8; dt += 2) {
+      for (int dt = 0; dt < DV / 8; dt += 2) {
         uint32_t vf[4];
         const int mid = lane >> 3;
-        ldmatrix_x4_trans(vf, vs_ + (wn * KEYS_W + kk * 16 + (mid & 1) * 8 + (lane & 7)) * LDS + (dt + (mid >> 1)) * 8);
+        ldmatrix_x4_trans(vf, vs_ + (wn * KEYS_W + kk * 16 + (mid & 1) * 8 + (lane & 7)) * LDSV + (dt + (mid >> 1)) * 8);
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           mma_bf16(o[mt][dt], pf[mt][kk], vf[0], vf[1]);
@@ -388,8 +439,8 @@ attention_mma_kernel(AttnArgs a) {
 
   // ---- merge the warps that shared rows, through shared memory (reuses the K/V stages)
   __syncthreads();
-  float* red_o = reinterpret_cast<float*>(Ks);      // [WARPS_N][BM][D]
-  float* red_m = red_o + WARPS_N * BM * D;          // [WARPS_N][BM]
+  float* red_o = reinterpret_cast<float*>(Ks);      // [WARPS_N][BM][DV]
+  float* red_m = red_o + WARPS_N * BM * DV;         // [WARPS_N][BM]
   float* red_l = red_m + WARPS_N * BM;              // [WARPS_N][BM]
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -401,16 +452,16 @@ attention_mma_kernel(AttnArgs a) {
         red_l[wn * BM + r] = l[mt][h];
       }
 #pragma unroll
-      for (int i = 0; i < D / 8; ++i) {
-        float* dst = red_o + ((long long)(wn * BM + r)) * D + i * 8 + (lane & 3) * 2;
+      for (int i = 0; i < DV / 8; ++i) {
+        float* dst = red_o + ((long long)(wn * BM + r)) * DV + i * 8 + (lane & 3) * 2;
         dst[0] = o[mt][i][h * 2 + 0];
         dst[1] = o[mt][i][h * 2 + 1];
       }
     }
   __syncthreads();
   const long long item = ((long long)tile * gridDim.y + kvh) * n_splits + split;
-  for (int i = threadIdx.x; i < BM * CHUNKS; i += NT_THREADS) {
-    const int r = i / CHUNKS, c = i % CHUNKS;
+  for (int i = threadIdx.x; i < BM * CHUNKS_V; i += NT_THREADS) {
+    const int r = i / CHUNKS_V, c = i % CHUNKS_V;
     const int R = row0 + r;
     float M = -INFINITY;
 #pragma unroll
@@ -421,7 +472,7 @@ attention_mma_kernel(AttnArgs a) {
       for (int w = 0; w < WARPS_N; ++w) {
         const float f = exp2f(red_m[w * BM + r] - M);
         L += red_l[w * BM + r] * f;
-        const float* src = red_o + ((long long)(w * BM + r)) * D + c * 8;
+        const float* src = red_o + ((long long)(w * BM + r)) * DV + c * 8;
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[e] += src[e] * f;
       }
@@ -435,10 +486,10 @@ attention_mma_kernel(AttnArgs a) {
         packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
         packed.z = pack_bf16(acc[4] * inv, acc[5] * inv);
         packed.w = pack_bf16(acc[6] * inv, acc[7] * inv);
-        *reinterpret_cast<uint4*>(a.out + (long long)(q_start + token) * a.out_stride + head * D + c * 8) = packed;
+        *reinterpret_cast<uint4*>(a.out + (long long)(q_start + token) * a.out_stride + head * DV + c * 8) = packed;
       }
     } else {
-      float* dst = a.part_o + (item * BM + r) * D + c * 8;
+      float* dst = a.part_o + (item * BM + r) * DV + c * 8;
 #pragma unroll
       for (int e = 0; e < 8; ++e) dst[e] = acc[e] * inv;
       if (c == 0) a.part_lse[item * BM + r] = L > 0.0f ? M + log2f(L) : -INFINITY;
@@ -458,15 +509,15 @@ attention_mma_kernel(AttnArgs a) {
   const long long item0 = ((long long)tile * gridDim.y + kvh) * n_splits;
   // all log-sum-exps first, in one parallel pass, into shared memory (the K/V stages are free)
   float* lse = reinterpret_cast<float*>(Ks);   // [n_splits][BM]
-  constexpr int LSE_CAPACITY = STAGES * BN * LDS * 2 * 2 / 4;
+  constexpr int LSE_CAPACITY = STAGES * BN * (LDS + LDSV) * 2 / 4;
   const bool lse_fits = n_splits * BM <= LSE_CAPACITY;
   if (lse_fits) {
     __syncthreads();  // everyone is done with red_o / red_m
     for (int i = threadIdx.x; i < n_splits * BM; i += NT_THREADS) lse[i] = __ldcg(a.part_lse + item0 * BM + i);
     __syncthreads();
   }
-  for (int i = threadIdx.x; i < BM * CHUNKS; i += NT_THREADS) {
-    const int r = i / CHUNKS, c = i % CHUNKS;
+  for (int i = threadIdx.x; i < BM * CHUNKS_V; i += NT_THREADS) {
+    const int r = i / CHUNKS_V, c = i % CHUNKS_V;
     const int R = row0 + r;
     if (R >= n_rows) continue;
     auto lse_at = [&](int z) { return lse_fits ? lse[z * BM + r] : __ldcg(a.part_lse + (item0 + z) * BM + r); };
@@ -477,7 +528,7 @@ attention_mma_kernel(AttnArgs a) {
 #pragma unroll 4
       for (int z = 0; z < n_splits; ++z) {   // independent loads: several are in flight at once
         const float w = exp2f(lse_at(z) - M);
-        const float4* src = reinterpret_cast<const float4*>(a.part_o + ((item0 + z) * BM + r) * D + c * 8);
+        const float4* src = reinterpret_cast<const float4*>(a.part_o + ((item0 + z) * BM + r) * DV + c * 8);
         const float4 lo = __ldcg(src), hi = __ldcg(src + 1);
         W += w;
         acc[0] += w * lo.x; acc[1] += w * lo.y; acc[2] += w * lo.z; acc[3] += w * lo.w;
@@ -491,7 +542,7 @@ attention_mma_kernel(AttnArgs a) {
     packed.y = pack_bf16(acc[2] * inv, acc[3] * inv);
     packed.z = pack_bf16(acc[4] * inv, acc[5] * inv);
     packed.w = pack_bf16(acc[6] * inv, acc[7] * inv);
-    *reinterpret_cast<uint4*>(a.out + (long long)(q_start + token) * a.out_stride + head * D + c * 8) = packed;
+    *reinterpret_cast<uint4*>(a.out + (long long)(q_start + token) * a.out_stride + head * DV + c * 8) = packed;
   }
   if (threadIdx.x == 0) *counter = 0;
 }
@@ -500,8 +551,8 @@ template <int WARPS_M, int WARPS_N, int MT>
 constexpr size_t smem_bytes() {
   constexpr int BM = 16 * MT * WARPS_M;
   constexpr int STAGES = WARPS_N > 1 ? 4 : 2;
-  constexpr size_t tiles = (size_t)(BM + 2 * STAGES * BN) * LDS * 2;
-  constexpr size_t merge = (size_t)BM * LDS * 2 + (size_t)WARPS_N * BM * (D + 2) * 4;
+  constexpr size_t tiles = ((size_t)(BM + STAGES * BN) * LDS + (size_t)STAGES * BN * LDSV) * 2;
+  constexpr size_t merge = (size_t)BM * LDS * 2 + (size_t)WARPS_N * BM * (DV + 2) * 4;
   return tiles > merge ? tiles : merge;
 }
 
@@ -523,7 +574,7 @@ int launch(const AttnArgs& a, int n_tiles, int kv_heads, int n_splits, cudaStrea
 
 }  // namespace
 
-constexpr int PREFILL_MT = D <= 64 ? 2 : 1;   // row tiles per warp in the prefill shape
+constexpr int PREFILL_MT = (D <= 64 && DV <= 64) ? 2 : 1;   // row tiles per warp in the prefill shape
 
 extern "C" int llm_attention_head_dim() { return D; }
 
@@ -536,7 +587,7 @@ extern "C" int llm_attention_prefill_rows() { return 64 * PREFILL_MT; }
 // log-sum-exps.
 #define LLM_ATTENTION_COUNTER_WORDS 4096
 extern "C" long long llm_attention_scratch_floats(int n_tiles, int kv_heads, int n_splits, int rows_per_tile) {
-  return LLM_ATTENTION_COUNTER_WORDS + (long long)n_tiles * kv_heads * n_splits * rows_per_tile * (D + 1);
+  return LLM_ATTENTION_COUNTER_WORDS + (long long)n_tiles * kv_heads * n_splits * rows_per_tile * (DV + 1);
 }
 
 // rows_per_tile: llm_attention_prefill_rows() (prefill shape) or 16 (decode shape).  `scratch` (llm_attention_scratch_floats
@@ -547,9 +598,14 @@ static int attention_mma_launch(const void* q, void* out, long long out_stride, 
                                 int head_dim, const int32_t* seq_q_start, const int32_t* seq_q_len,
                                 const int32_t* seq_kv_len, const int32_t* tile_seq, const int32_t* tile_index,
                                 int n_tiles, int rows_per_tile, int n_splits, float* scratch, int q_heads,
-                                float scale, int window, cudaStream_t stream) {
+                                float scale, int window, cudaStream_t stream, float cap = 0.0f) {
   if (n_tiles <= 0) return 0;
   if (out_stride % 8) return ERR_BAD_ALIGN;
+#ifdef SCORE_CAP
+  if (!(cap > 0.0f)) return ERR_BAD_SIZE;
+#else
+  if (cap != 0.0f) return ERR_BAD_SIZE;      // this library applies no cap
+#endif
   if (head_dim != D || q_heads % kv_heads || n_splits < 1 || n_splits > 65535 || kv_heads > 65535) return ERR_BAD_SIZE;
   if (n_splits > 1 && !scratch) return ERR_BAD_SIZE;
   if (n_splits > 1 && (long long)n_tiles * kv_heads > LLM_ATTENTION_COUNTER_WORDS) return ERR_BAD_SIZE;
@@ -567,7 +623,7 @@ static int attention_mma_launch(const void* q, void* out, long long out_stride, 
   a.tile_index = tile_index;
   a.counters = reinterpret_cast<int*>(scratch);
   a.part_o = scratch ? scratch + LLM_ATTENTION_COUNTER_WORDS : nullptr;
-  a.part_lse = scratch ? a.part_o + (long long)n_tiles * kv_heads * n_splits * rows_per_tile * D : nullptr;
+  a.part_lse = scratch ? a.part_o + (long long)n_tiles * kv_heads * n_splits * rows_per_tile * DV : nullptr;
   a.q_heads = q_heads;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.window = window;
@@ -575,6 +631,8 @@ static int attention_mma_launch(const void* q, void* out, long long out_stride, 
   a.out_scale = out_scale;
   a.bias = bias;
   a.bias_len = bias_len;
+  a.scale_over_cap = cap > 0.0f ? scale / cap : 0.0f;
+  a.cap_log2 = cap * 1.4426950408889634f;
   if (rows_per_tile == 64 * PREFILL_MT) return launch<4, 1, PREFILL_MT>(a, n_tiles, kv_heads, n_splits, stream);
   if (rows_per_tile == 16) return launch<1, 4, 1>(a, n_tiles, kv_heads, n_splits, stream);
   return ERR_BAD_SIZE;
@@ -588,13 +646,32 @@ extern "C" int llm_attention_mma(const void* q, void* out, void* k_base, void* v
                                  float scale, int window, cudaStream_t stream) {
 #ifdef DISTANCE_BIAS
   return ERR_BAD_SIZE;   // this library is the variant with a bias: llm_attention_mma_bias
+#elif defined(SCORE_CAP)
+  return ERR_BAD_SIZE;   // this library is the variant with a cap: llm_attention_mma_general
 #else
-  return attention_mma_launch(q, out, (long long)q_heads * D, 1.0f, nullptr, 0, k_base, v_base, block_table, page_stride,
+  return attention_mma_launch(q, out, (long long)q_heads * DV, 1.0f, nullptr, 0, k_base, v_base, block_table, page_stride,
                               table_stride, page_tokens, kv_heads, head_dim, seq_q_start, seq_q_len, seq_kv_len,
                               tile_seq, tile_index, n_tiles, rows_per_tile, n_splits, scratch, q_heads, scale, window,
                               stream);
 #endif
 }
+
+#ifndef DISTANCE_BIAS
+// Value heads of `v_dim` entries (this library's V_DIM) beside key heads of `head_dim`, and `cap` (0: none; a
+// library built with -DSCORE_CAP takes a positive one): score <- cap * tanh(score * scale / cap).
+extern "C" int llm_attention_mma_general(const void* q, void* out, void* k_base, void* v_base, const int32_t* block_table,
+                                         long long page_stride, int table_stride, int page_tokens, int kv_heads,
+                                         int head_dim, int v_dim, const int32_t* seq_q_start, const int32_t* seq_q_len,
+                                         const int32_t* seq_kv_len, const int32_t* tile_seq, const int32_t* tile_index,
+                                         int n_tiles, int rows_per_tile, int n_splits, float* scratch, int q_heads,
+                                         float scale, int window, float cap, cudaStream_t stream) {
+  if (v_dim != DV) return ERR_BAD_SIZE;
+  return attention_mma_launch(q, out, (long long)q_heads * DV, 1.0f, nullptr, 0, k_base, v_base, block_table, page_stride,
+                              table_stride, page_tokens, kv_heads, head_dim, seq_q_start, seq_q_len, seq_kv_len,
+                              tile_seq, tile_index, n_tiles, rows_per_tile, n_splits, scratch, q_heads, scale, window,
+                              stream, cap);
+}
+#endif
 
 #ifdef DISTANCE_BIAS
 // The variant with a bias by distance: `bias` float32 [q_heads][bias_len], `out` rows `out_stride`

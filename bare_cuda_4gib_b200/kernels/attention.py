@@ -28,24 +28,33 @@ TC_HEAD_DIMS = (64, 128)      # head sizes the tcgen05 prefill kernel and the de
 DECODE_MAX_TILES = 65535 // 4 # (tiles x kv heads) up to which the cluster decode kernel runs
 
 
-def supports(head_dim: int) -> bool:
-    return head_dim % 16 == 0 and 16 <= head_dim <= 128
+def supports(head_dim: int, v_dim: Optional[int] = None) -> bool:
+    v_dim = head_dim if v_dim is None else v_dim
+    return head_dim % 16 == 0 and 16 <= head_dim <= 128 and v_dim % 16 == 0 and 16 <= v_dim <= 128
 
 
 def defines(head_dim: int):
     return (f"-DHEAD_DIM={head_dim}",)
 
 
-def lib(head_dim: int, distance_bias: bool = False):
+def lib(head_dim: int, distance_bias: bool = False, v_dim: Optional[int] = None, capped: bool = False):
     """The mma.sync kernel's library for this head size; with `distance_bias` the variant that adds
-    a bias by distance to every score (entry point `llm_attention_mma_bias`)."""
-    key = (head_dim, "bias") if distance_bias else head_dim
+    a bias by distance to every score (entry point `llm_attention_mma_bias`); with `v_dim` the one for
+    value heads of another size than the key heads', with `capped` the one that caps the scaled scores
+    with a tanh (entry point `llm_attention_mma_general` for both)."""
+    v_dim = None if v_dim == head_dim else v_dim
+    key = (head_dim, "bias") if distance_bias else ((head_dim, v_dim, capped) if (v_dim or capped) else head_dim)
     l = _libs.get(key)
     if l is None:
-        l = build.load_library("attention_mma.cu", defines(head_dim) + (("-DDISTANCE_BIAS",) if distance_bias else ()))
+        flags = defines(head_dim) + (("-DDISTANCE_BIAS",) if distance_bias else ())
+        flags += ((f"-DV_DIM={v_dim}",) if v_dim else ()) + (("-DSCORE_CAP",) if capped else ())
+        l = build.load_library("attention_mma.cu", flags)
         P, I, L, F = c_void_p, c_int, c_longlong, c_float
         l.llm_attention_mma.argtypes = [P, P, P, P, P, L, I, I, I, I, P, P, P, P, P, I, I, I, P, I, F, I, P]
         l.llm_attention_mma.restype = c_int
+        if not distance_bias:
+            l.llm_attention_mma_general.argtypes = [P, P, P, P, P, L, I, I, I, I, I, P, P, P, P, P, I, I, I, P, I, F, I, F, P]
+            l.llm_attention_mma_general.restype = c_int
         if distance_bias:
             l.llm_attention_mma_bias.argtypes = [P, P, L, F, P, I, P, P, P, L, I, I, I, I, P, P, P, P, P, I, I, I, P, I,
                                                  F, I, P]
@@ -89,20 +98,26 @@ def decode_lib(head_dim: int):
 
 
 class AttentionPlan:
-    def __init__(self, head_dim: int, heads: int, kv_heads: int, distance_bias: bool = False):
-        """`distance_bias`: attention whose scores get a bias by distance; only the mma.sync kernel
-        has that variant, so the plan uses it for every step shape."""
+    def __init__(self, head_dim: int, heads: int, kv_heads: int, distance_bias: bool = False,
+                 v_dim: Optional[int] = None, softcap: float = 0.0):
+        """`distance_bias`: attention whose scores get a bias by distance; `v_dim`: value heads of a size of
+        their own; `softcap` > 0: scaled scores capped with a tanh.  Only the mma.sync kernel has these
+        variants, so such a plan uses it for every step shape."""
         self.head_dim, self.heads, self.kv_heads = head_dim, heads, kv_heads
         self.group = heads // kv_heads
         self.distance_bias = distance_bias
-        self.lib = lib(head_dim, distance_bias)
+        self.v_dim = head_dim if v_dim is None else int(v_dim)
+        self.softcap = float(softcap or 0.0)
+        self.general = self.v_dim != head_dim or self.softcap > 0.0      # what only the mma.sync kernel computes
+        self.lib = lib(head_dim, distance_bias, self.v_dim, self.softcap > 0.0)
         self.prefill_rows = int(self.lib.llm_attention_prefill_rows())
         self.tc = None
-        if head_dim in TC_HEAD_DIMS and not distance_bias:
+        if head_dim in TC_HEAD_DIMS and not distance_bias and not self.general:
             self.tc = tc_lib(head_dim)
             self.prefill_rows = int(self.tc.llm_attention_tc_rows())
         self.decode = None
-        if head_dim in TC_HEAD_DIMS and not distance_bias and not os.environ.get("BARE_CUDA_B200_NO_DECODE_ATTENTION"):
+        if head_dim in TC_HEAD_DIMS and not distance_bias and not self.general \
+                and not os.environ.get("BARE_CUDA_B200_NO_DECODE_ATTENTION"):
             self.decode = decode_lib(head_dim)
         self._host = None
         self._dev = None
@@ -166,20 +181,22 @@ class AttentionPlan:
     def scratch(self, ctx, floats: int, device) -> torch.Tensor:
         """Scratch for split keys; a split step has at most (2 * sm_count()) + tiles * kv_heads items."""
         if self._scratch is None or self._scratch.numel() < floats:
-            most = COUNTER_WORDS + ((2 * sm_count()) + (ctx.max_seqs + 8) * self.kv_heads) * 16 * (self.head_dim + 1)
+            most = COUNTER_WORDS + ((2 * sm_count()) + (ctx.max_seqs + 8) * self.kv_heads) * 16 * (max(self.head_dim, self.v_dim) + 1)
             self._scratch = torch.zeros(max(floats, most), dtype=torch.float32, device=device)   # counters start at zero
         return self._scratch
 
 
-def plan_for(head_dim: int, heads: int, kv_heads: int, distance_bias: bool = False) -> Optional[AttentionPlan]:
-    if not supports(head_dim):
+def plan_for(head_dim: int, heads: int, kv_heads: int, distance_bias: bool = False, v_dim: Optional[int] = None,
+             softcap: float = 0.0) -> Optional[AttentionPlan]:
+    if not supports(head_dim, v_dim) or (distance_bias and (softcap or (v_dim or head_dim) != head_dim)):
         return None
-    return AttentionPlan(head_dim, heads, kv_heads, distance_bias)
+    return AttentionPlan(head_dim, heads, kv_heads, distance_bias, v_dim, softcap)
 
 
 def step_tiles(ctx, plan: AttentionPlan):
     """The step's row tiles for this head grouping: built once per step and shared by all layers."""
-    key = ("attention_tiles", plan.group, plan.kv_heads, plan.head_dim, plan.distance_bias)
+    key = ("attention_tiles", plan.group, plan.kv_heads, plan.head_dim, plan.distance_bias, plan.prefill_rows,
+           plan.decode is not None)
     cached = ctx.extras.get(key)
     if cached is not None:
         return cached
@@ -278,6 +295,16 @@ def run(ctx, plan: AttentionPlan, q: torch.Tensor, out: torch.Tensor, cache: Cac
     if n_splits > 1:
         floats = plan.lib.llm_attention_scratch_floats(n_tiles, plan.kv_heads, n_splits, rows_per_tile)
         scratch_ptr = plan.scratch(ctx, int(floats), q.device).data_ptr()
+    if plan.general:
+        if cache.v_dim != plan.v_dim or cache.head_dim != plan.head_dim:
+            raise KernelLaunchError("attention_mma: the cache's head sizes are not the plan's")
+        _check(plan.lib.llm_attention_mma_general(
+            q.data_ptr(), out.data_ptr(), cache.k_ptr, cache.v_ptr, cache.block_table.data_ptr(), cache.page_stride,
+            cache.table_stride, cache.page_tokens, cache.kv_heads, cache.head_dim, cache.v_dim, ctx.seq_q_start.data_ptr(),
+            ctx.seq_q_len.data_ptr(), ctx.seq_kv_len.data_ptr(), tile_seq.data_ptr(), tile_index.data_ptr(), n_tiles,
+            rows_per_tile, n_splits, scratch_ptr, plan.heads, scale, window, plan.softcap, ctx.stream),
+            "attention_mma (value size, score cap)")
+        return
     _check(plan.lib.llm_attention_mma(
         q.data_ptr(), out.data_ptr(), cache.k_ptr, cache.v_ptr, cache.block_table.data_ptr(), cache.page_stride,
         cache.table_stride, cache.page_tokens, cache.kv_heads, cache.head_dim, ctx.seq_q_start.data_ptr(),

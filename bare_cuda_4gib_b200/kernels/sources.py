@@ -15,6 +15,9 @@ def all_libraries():
              ("gemm_tcgen05.cu", ("-DGROUPED_UP_RELU2",))]
     jobs += [("attention_mma.cu", (f"-DHEAD_DIM={d}",)) for d in ATTENTION_HEAD_DIMS]
     jobs += [("attention_mma.cu", (f"-DHEAD_DIM={d}", "-DDISTANCE_BIAS")) for d in ATTENTION_HEAD_DIMS]
+    # value heads of their own size and capped scores, as the Gurolix presets have them
+    jobs += [("attention_mma.cu", ("-DHEAD_DIM=128", "-DV_DIM=64")), ("attention_mma.cu", ("-DHEAD_DIM=128", "-DV_DIM=64", "-DSCORE_CAP")),
+             ("attention_mma.cu", ("-DHEAD_DIM=128", "-DSCORE_CAP")), ("attention_mma.cu", ("-DHEAD_DIM=16", "-DV_DIM=32", "-DSCORE_CAP"))]
     jobs += [("attention_tcgen05.cu", (f"-DHEAD_DIM={d}",)) for d in (64, 128)]
     jobs += [("attention_decode.cu", (f"-DHEAD_DIM={d}",)) for d in (64, 128)]
     jobs += [("diff_attention.cu", (f"-DDA_DQ={d}", f"-DDA_DV={v}")) for d, v in DIFF_ATTENTION_SIZES]

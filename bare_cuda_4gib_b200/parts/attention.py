@@ -216,8 +216,9 @@ class GeneralAttention(Part):
     l v_source of the same token, l the scalar tensor `v_lambda`.
 
     One product makes [q | k | v]; one kernel adds the biases, norms, turns, mixes and caches; then the
-    engine's tensor-core attention kernels run where they take the shape (equal key and value sizes, no
-    cap), the plain kernel everywhere else.
+    engine's tensor-core attention kernels run in bfloat16 steps (all three for equal key and value sizes
+    without a cap, the mma.sync kernel built for the value size and the cap otherwise), the plain kernel in
+    float32 steps and for sizes that are no multiples of 16 up to 128.
 
     params: `hidden`, `heads`, `kv_heads`, `dim`, `vdim`, `scale`, `eps`, `bias` (bool), `qk_norm` (bool),
     `softcap` (None: no cap), `window` (None: every key), `v_mix` (None | "source" | "mix"), `position`.
@@ -287,9 +288,11 @@ class GeneralAttention(Part):
         self.halves = bool(getattr(self.position, "halves", False))
         self.magnitude = float(getattr(self.position, "magnitude", 1.0))
         self.fast = None
-        if dtype == torch.bfloat16 and device.type == "cuda" and self.vdim == self.dim and not self.softcap:
+        if dtype == torch.bfloat16 and device.type == "cuda":
+            # equal head sizes without a cap: the engine's tcgen05 prefill, cluster decode and mma.sync kernels;
+            # otherwise the mma.sync kernel built for this value size and with the cap (sizes it takes)
             from ..kernels import attention as fast
-            self.fast = fast.plan_for(self.dim, self.heads, self.kv_heads)
+            self.fast = fast.plan_for(self.dim, self.heads, self.kv_heads, False, self.vdim, self.softcap)
 
     def plan_step(self, ctx) -> None:
         if self.fast is not None and ctx.use_fast_attention:

@@ -186,9 +186,10 @@ SETTLE_SECONDS = 0.1      # pause between putting the prompts into the cache and
 
 
 def design_main(args) -> int:
-    """`--design dopudra`, `zadurax` or `pudulorn`: one JSON line with, per size, a prefill step of `--prefill-tokens` tokens and decode
+    """`--design dopudra`, `zadurax`, `pudulorn` or `gurolix`: one JSON line with, per size, a prefill step of `--prefill-tokens` tokens and decode
     steps at `--batch` requests of `--context` positions for the design and for the Llama decoder of the same
-    width, both with `--design-layers` layers, seeded random weights, bfloat16, CUDA events around the steps."""
+    width (for `gurolix`: the Pudulorn decoder, the engine's other design with a mixture of experts), both with
+    `--design-layers` layers, seeded random weights, bfloat16, CUDA events around the steps."""
     import torch
 
     from bare_cuda_4gib_b200.engine.engine import LLMEngine
@@ -257,12 +258,16 @@ def design_main(args) -> int:
                 "weight_bytes": weights}
 
     sizes = []
-    for name, closest in ((f"{args.design}-2048", "tinyllama"), (f"{args.design}-4096", "llama2-7b")):
+    beside = {"gurolix": ("pudulorn-2048", "pudulorn-4096")}.get(args.design, ("tinyllama", "llama2-7b"))
+    for name, closest in ((f"{args.design}-2048", beside[0]), (f"{args.design}-4096", beside[1])):
         if args.preset not in ("tinyllama", name):       # --preset NAME: that size only
             continue
         layers = PRESETS[name]["layers"][: args.design_layers]
         mine = measure(preset_config(name, layers=layers))
-        theirs = measure(preset_config(closest, num_hidden_layers=len(layers), vocab_size=PRESETS[name]["vocab"]))
+        if "architecture" in PRESETS[closest]:
+            theirs = measure(preset_config(closest, layers=PRESETS[closest]["layers"][: len(layers)]))
+        else:
+            theirs = measure(preset_config(closest, num_hidden_layers=len(layers), vocab_size=PRESETS[name]["vocab"]))
         sizes.append({"preset": name, "layers": len(layers), "width": PRESETS[name]["width"], **mine,
                       "closest": {"preset": closest, **theirs}})
     print(json.dumps({"design": args.design, "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random "
@@ -288,7 +293,7 @@ def main() -> int:
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--only", default="", choices=["", "prefill", "decode"],
                     help="profiling aid: run just the prefill step or just the decode steps and print their time")
-    ap.add_argument("--design", default="", choices=["", "dopudra", "zadurax", "pudulorn"],
+    ap.add_argument("--design", default="", choices=["", "dopudra", "zadurax", "pudulorn", "gurolix"],
                     help="instead of the default workload: prefill and decode throughput of this design at layer sizes "
                          "of real models, beside the Llama decoder at equal width, layer count and vocabulary")
     ap.add_argument("--design-layers", type=int, default=8, help="layers of both models in a --design run")
