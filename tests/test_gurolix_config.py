@@ -39,8 +39,8 @@ def test_caches_states_and_value_lenders():
     # a Mamba-2 layer keeps its matrix state and the convolution's last taps - 1 inputs, no pages
     assert [d.kv for d in demands[0]] == [None, None]
     assert demands[0][0].state == StateRequest((4, 16, 8), torch.float32)
-    assert demands[0][1].state == StateRequest((3, 32 + 2 * 2 * 16), torch.float32)
-    assert demands[4][1].state == StateRequest((1, 32 + 2 * 8), torch.float32)
+    assert demands[0][1].state == StateRequest((4, 32 + 2 * 2 * 16), torch.float32)      # a ring of `taps` entries
+    assert demands[4][1].state == StateRequest((2, 32 + 2 * 8), torch.float32)
     # attention layers keep pages with value heads of their own size, and no state
     assert demands[1][0].kv == KVCacheRequest(2, 16, None, v_head_dim=24) and demands[1][0].state is None
     assert demands[5][0].kv == KVCacheRequest(2, 8, None, v_head_dim=24)

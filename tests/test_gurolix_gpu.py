@@ -51,6 +51,9 @@ ALONE = {
     "mamba2_group_per_head_long_taps": [U.mamba2(2, 40, 8, 2, 7, 5)],
     "mamba2_wide_state": [U.mamba2(2, 8, 200, 1, 3, 2)],
     "mamba2_twice": [U.mamba2(2, 16, 16, 2, 2, 1), U.mamba2(4, 8, 8, 1, 4, 2)],
+    "mamba2_norm_parts_inside_heads": [U.mamba2(2, 24, 16, 1, 3, 6)],                  # a head spans three parts of the norm
+    "mamba2_part_over_two_groups": [U.mamba2(8, 8, 16, 4, 4, 2)],                      # a part's heads read two groups each
+    "mamba2_wide_heads": [U.mamba2(2, 320, 8, 2, 2, 2)],                               # more value columns than a block has threads
     "experts_with_identity_and_groups": [U.attention(2, 1, 16, 16, 8, mlp=U.moe(5, 2, 24, identity=1, groups=(3, 2)))],
     "experts_mostly_identity": [U.mamba2(2, 8, 8, 1, 2, 1, mlp=U.moe(2, 3, 16, identity=6, groups=(4, 2)))],
     "experts_one_of_three_plain_router": [U.attention(2, 2, 16, 16, 8, mlp=U.moe(3, 1, 32))],
@@ -154,12 +157,14 @@ def test_ungated_expert_products_plain_and_on_tensor_cores(n, experts, identity,
         assert err < 2e-2, (tc, err)
 
 
-def test_gated_step_kernel_alone():
-    """Gate, norm behind the sublayer, add, depth sum and the next norm against plain arithmetic, in pieces and at once."""
+@pytest.mark.parametrize("rows,width", [(37, 200), (5, 202), (9, 2048), (70, 4096), (3, 6000)])
+def test_gated_step_kernel_alone(rows, width):
+    """Gate, norm behind the sublayer, add, depth sum and the next norm against plain arithmetic: widths that go
+    entry by entry, in pieces of four, and in a wide block for few rows."""
     from bare_cuda_4gib_b200.kernels import gated_sandwich as GS
     from bare_cuda_4gib_b200.kernels.lib import Partials
     g = torch.Generator().manual_seed(2)
-    rows, width, entries = 37, 200, 4
+    entries = 4
     x = torch.randn(rows, width, generator=g)
     y = torch.randn(3, rows, width, generator=g)
     gate, bias = torch.randn(rows, width, generator=g), torch.randn(width, generator=g)
@@ -168,29 +173,32 @@ def test_gated_step_kernel_alone():
     hist = torch.randn(entries, rows, width, generator=g)
     unit = lambda v, eps: v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
     d = torch.float64
-    new = x.to(d) + unit(y.to(d).sum(0) * torch.sigmoid(gate.to(d) + bias.to(d)), 1e-5) * post.to(d)
-    mixed = (mix[:-1].to(d)[:, None, None] * hist[:-1].to(d)).sum(0) + mix[-1].to(d) * new
-    want = unit(mixed, 1e-6) * nxt.to(d)
-    for gate_dtype in (torch.float32, torch.bfloat16):
+    for gate_dtype, out_dtype in ((torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)):
         res, hs = x.clone().cuda(), hist.clone().cuda()
         gt = gate.to(gate_dtype)
-        new_g = x.to(d) + unit(y.to(d).sum(0) * torch.sigmoid(gt.to(d) + bias.to(d)), 1e-5) * post.to(d)
-        out = torch.empty(rows, width, device="cuda")
+        new = x.to(d) + unit(y.to(d).sum(0) * torch.sigmoid(gt.to(d) + bias.to(d)), 1e-5) * post.to(d)
+        out = torch.empty(rows, width, dtype=out_dtype, device="cuda")
         delta = GS.GatedDelta(Partials(y.cuda(), 3), gt.cuda(), bias.cuda(), post.cuda(), 1e-5,
                               GS.DepthMix(hs, entries - 1, mix.cuda()))
         GS.step(res, delta, nxt.cuda(), out, 1e-6, rows)
-        mixed_g = (mix[:-1].to(d)[:, None, None] * hist[:-1].to(d)).sum(0) + mix[-1].to(d) * new_g
-        assert H.row_error(hs[entries - 1], new_g) < 1e-5           # the layer's own result is kept before the sum
-        assert H.row_error(res, mixed_g) < 1e-5
-        assert H.row_error(out, unit(mixed_g, 1e-6) * nxt.to(d)) < 1e-5
-    assert H.row_error(out, want) < 2e-2
+        mixed = (mix[:-1].to(d)[:, None, None] * hist[:-1].to(d)).sum(0) + mix[-1].to(d) * new
+        assert H.row_error(hs[entries - 1], new) < 1e-5           # the layer's own result is kept before the sum
+        assert torch.equal(hs[: entries - 1].cpu(), hist[: entries - 1])
+        assert H.row_error(res, mixed) < 1e-5
+        assert H.row_error(out, unit(mixed, 1e-6) * nxt.to(d)) < (1e-5 if out_dtype == torch.float32 else 1e-2)
+    # entry 0 alone (the embedding's output is kept, nothing is added or summed), then the norm
+    res, hs = x.clone().cuda(), hist.clone().cuda()
+    out = torch.empty(rows, width, device="cuda")
+    GS.step(res, GS.GatedDelta(None, None, None, None, 0.0, GS.DepthMix(hs, 0, None)), nxt.cuda(), out, 1e-6, rows)
+    assert torch.equal(res.cpu(), x) and torch.equal(hs[0].cpu(), x) and torch.equal(hs[1:].cpu(), hist[1:])
+    assert H.row_error(out, unit(x.to(d), 1e-6) * nxt.to(d)) < 1e-5
     # only some rows, nothing pending: the norm of the wanted rows, the stream untouched
     res = x.clone().cuda()
-    index = torch.tensor([5, 0, 36], dtype=torch.int32, device="cuda")
+    index = torch.tensor([min(5, rows - 1), 0, rows - 1], dtype=torch.int32, device="cuda")
     out = torch.empty(3, width, dtype=torch.bfloat16, device="cuda")
     GS.step(res, None, nxt.cuda(), out, 1e-6, 3, index)
     assert torch.equal(res.cpu(), x)
-    assert H.row_error(out, (unit(x.to(d), 1e-6) * nxt.to(d))[[5, 0, 36]]) < 1e-2
+    assert H.row_error(out, (unit(x.to(d), 1e-6) * nxt.to(d))[index.cpu().long()]) < 1e-2
 
 
 # ------------------------------------------------------------------ every cutting, two configs
