@@ -21,8 +21,8 @@ def lib():
         l.llm_mamba2_operands.argtypes = [P, I, L, P, P, I, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, P]
         l.llm_mamba2_finish.argtypes = [P, P, P, P, I, L, P, P, L, I, I, I, I, F, P]
         l.llm_mamba2_ring_write.argtypes = [P, I, L, P, I, I, P, P, P, P, I, P]
-        l.llm_mamba2_step.argtypes = [P, I, L, P, P, I, P, P, P, P, P, P, P, L, P, P, P, I, I, I, I, I, I, F, I, P]
-        l.llm_mamba2_step_shared_bytes.argtypes = [I, I, I, I, I]
+        l.llm_mamba2_step.argtypes = [P, I, L, P, P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P]
+        l.llm_mamba2_step_shared_bytes.argtypes = [I, I, I, I]
         l.llm_mamba2_step_shared_bytes.restype = c_longlong
         for name in ("llm_mamba2_operands", "llm_mamba2_finish", "llm_mamba2_ring_write", "llm_mamba2_step"):
             getattr(l, name).restype = c_int
@@ -69,24 +69,24 @@ def ring_write(ctx, u: torch.Tensor, ring: torch.Tensor, taps: int, channels: in
 STEP_MAX_SHARED = 160 * 1024
 
 
-def step_takes(heads: int, vdim: int, state: int, groups: int, parts: int) -> bool:
-    """Whether the one-kernel form for steps of one token per request takes these sizes: the norm's parts hold
-    whole heads, and a part's channels fit in shared memory."""
-    if heads % parts or heads % groups:
+def step_takes(heads: int, vdim: int, state: int, groups: int) -> bool:
+    """Whether the form for steps of one token per request takes these sizes (a head's channels fit in shared memory)."""
+    if heads % groups:
         return False
-    need = int(lib().llm_mamba2_step_shared_bytes(heads, vdim, state, groups, parts))
+    need = int(lib().llm_mamba2_step_shared_bytes(heads, vdim, state, groups))
     return 0 < need <= STEP_MAX_SHARED
 
 
-def step(ctx, u: torch.Tensor, conv_w, conv_b, ring, dt_bias, a_log, d_skip, norm_w, state, out: torch.Tensor,
-         heads: int, vdim: int, state_size: int, groups: int, parts: int, eps: float, write_ring: bool) -> None:
-    """All of a Mamba-2 mixer between its two projections for a step of one token per request: convolution
-    (and the ring's update), step sizes, the state updated in place, D term, gate, norm in parts, weight."""
-    _dev(u, conv_w, conv_b, ring, dt_bias, a_log, d_skip, norm_w, state, out)
-    if u.dtype != out.dtype or state.dtype != torch.float32 or ring.dtype != torch.float32:
-        raise TypeError("mamba2 step: element types not as the kernel needs")
+def step(ctx, u: torch.Tensor, conv_w, conv_b, ring, dt_bias, a_log, state, scanned: torch.Tensor, xc: torch.Tensor,
+         heads: int, vdim: int, state_size: int, groups: int, write_ring: bool) -> None:
+    """A step of one token per request, a block per (request, head): convolution (and the ring's update), step
+    size and decay, the state updated in place; scanned [rows, heads * vdim] = S^T C and xc = x, both float32,
+    for `finish`."""
+    _dev(u, conv_w, conv_b, ring, dt_bias, a_log, state, scanned, xc)
+    if state.dtype != torch.float32 or ring.dtype != torch.float32 or scanned.dtype != torch.float32 or xc.dtype != torch.float32:
+        raise TypeError("mamba2 step: states and results must be float32")
     _check(lib().llm_mamba2_step(
         u.data_ptr(), dtype_code(u.dtype), u.stride(0), conv_w.data_ptr(), conv_b.data_ptr(), conv_w.shape[1],
-        ring.data_ptr(), dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), norm_w.data_ptr(), state.data_ptr(),
-        out.data_ptr(), out.stride(0), ctx.positions.data_ptr(), ctx.seq_slot.data_ptr(), ctx.seq_q_start.data_ptr(),
-        ctx.n_seqs, heads, vdim, state_size, groups, parts, float(eps), 1 if write_ring else 0, ctx.stream), "mamba2_step")
+        ring.data_ptr(), dt_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(), scanned.data_ptr(), xc.data_ptr(),
+        ctx.positions.data_ptr(), ctx.seq_slot.data_ptr(), ctx.seq_q_start.data_ptr(), ctx.n_seqs, heads, vdim, state_size,
+        groups, 1 if write_ring else 0, ctx.stream), "mamba2_step")

@@ -10,8 +10,8 @@ then y * silu(z), an RMS norm in `norm_groups` equal parts (each by its own root
 weight, and the output projection.  A request keeps S as a float32 state [heads, state, vdim] and the
 convolution's last inputs as a second one (a ring of `taps` entries by position); the walk over a
 step's tokens is the engine's state scan (`kernels.linear_attention.scan`) with one decay per token and
-head, fed with float32 operands; the kernels of csrc/mamba2.cu come before and after it.  A step of one
-token per request runs one kernel instead (where the norm's parts hold whole heads).
+head, fed with float32 operands; the kernels of csrc/mamba2.cu come before and after it.  In a step of one
+token per request one kernel with a block per (request, head) stands for operands, ring and scan.
 
 params: `hidden`, `heads`, `vdim`, `state`, `groups`, `taps`, `norm_groups`, `eps`.
 tensors: `in` [2 * heads * vdim + 2 * groups * state + heads, hidden], `conv` [channels, taps], `conv_bias`
@@ -76,8 +76,7 @@ class Mamba2(Part):
         f = lambda x: x.to(torch.float32).contiguous()
         self.conv_w, self.conv_b = f(t["conv"]), f(t["conv_bias"])
         self.dt_bias, self.a_log, self.d_skip, self.norm_w = f(t["dt_bias"]), f(t["A_log"]), f(t["D"]), f(t["norm"])
-        self.one_kernel = device.type == "cuda" and MK.step_takes(self.heads, self.vdim, self.state, self.groups,
-                                                                   self.norm_groups)
+        self.one_step = device.type == "cuda" and MK.step_takes(self.heads, self.vdim, self.state, self.groups)
 
     def forward(self, ctx, call, h):
         n, H, P, N = ctx.n_tokens, self.heads, self.vdim, self.state
@@ -85,20 +84,21 @@ class Mamba2(Part):
         u = self.proj.forward(ctx, h, n, ctx.dtype, "mixer_in").tensor
         state, ring = call.states[0], call.states[1]
         out = ctx.ws.get("mixer_act", (n, self.inner), ctx.dtype)
-        if ctx.max_q_len == 1 and self.one_kernel:
-            MK.step(ctx, u, self.conv_w, self.conv_b, ring, self.dt_bias, self.a_log, self.d_skip, self.norm_w, state, out,
-                    H, P, N, self.groups, self.norm_groups, self.eps, call.writes_cache)
+        xc = ctx.ws.get("mamba2_x", (n, self.inner), f32)
+        scanned = ctx.ws.get("mamba2_scan", (n, self.inner), f32)
+        if ctx.max_q_len == 1 and self.one_step:
+            MK.step(ctx, u, self.conv_w, self.conv_b, ring, self.dt_bias, self.a_log, state, scanned, xc, H, P, N,
+                    self.groups, call.writes_cache)
+            MK.finish(ctx, scanned, xc, self.d_skip, u[:, : self.inner], self.norm_w, out, P, self.norm_groups, self.eps)
             return self.o.forward(ctx, out, n, torch.float32, "mixer_out", allow_partials=True)
         qf = ctx.ws.get("mamba2_q", (n, H * N), f32)
         kf = ctx.ws.get("mamba2_k", (n, H * N), f32)
         vf = ctx.ws.get("mamba2_v", (n, self.inner), f32)
-        xc = ctx.ws.get("mamba2_x", (n, self.inner), f32)
         decay = ctx.ws.get("mamba2_decay", (n, H), f32)
         MK.operands(ctx, u, self.conv_w, self.conv_b, ring, self.dt_bias, self.a_log, qf, kf, vf, xc, decay, H, P, N,
                     self.groups)
         if call.writes_cache:
             MK.ring_write(ctx, u[:, self.inner: self.inner + self.conv_channels], ring, self.taps, self.conv_channels)
-        scanned = ctx.ws.get("mamba2_scan", (n, self.inner), f32)
         LA.scan(ctx, qf, kf, vf, decay, "token", state, scanned, H, N, P)
         MK.finish(ctx, scanned, xc, self.d_skip, u[:, : self.inner], self.norm_w, out, P, self.norm_groups, self.eps)
         return self.o.forward(ctx, out, n, torch.float32, "mixer_out", allow_partials=True)
