@@ -4,9 +4,10 @@
     layers: [{type: "attention" | "attention_2" | "mamba2", mixer: {...}, mlp: {...} | null}, ...]
 
     attention mixer:    heads, kv_heads, dim, vdim, scale, v_mix, rot.{dims, base}
-                        (queries and keys are normed per head; plain rotation)
+                        (queries and keys are normed per head)
     attention_2 mixer:  heads, kv_heads, dim, vdim, scale, softcap, v_mix, rot.{dims, base,
-                        scaling.{factor, low, high, original}}
+                        scaling.{factor, low, high, original}}  (no norms)
+                        (`softcap` and `rot.scaling` are applied wherever an attention mixer states them)
     mamba2 mixer:       heads, vdim, state, groups, conv, norm_groups
     mlp:                kind "moe", expert.ff, router.{experts, top, identity, groups.{count, keep}}
 
@@ -27,7 +28,7 @@ from .dopudra import _get
 MIXER_TYPES = ("attention", "attention_2", "mamba2")
 
 
-def _rotation(rot, where: str, most: int, scaled: bool) -> None:
+def _rotation(rot, where: str, most: int) -> None:
     dims = _get(rot, "dims", where)
     _get(rot, "base", where, float)
     if dims % 2:
@@ -36,8 +37,6 @@ def _rotation(rot, where: str, most: int, scaled: bool) -> None:
         raise ConfigError(f"config.json: '{where}dims' {dims} exceeds the {most} entries it is applied to")
     sc = rot.get("scaling")
     if sc is not None:
-        if not scaled:
-            raise ConfigError(f"config.json: '{where}scaling' is not part of this mixer")
         for key in ("factor", "low", "high", "original"):
             _get(sc, key, where + "scaling.", float)
         if not sc["high"] > sc["low"]:
@@ -51,13 +50,11 @@ def _attention(m, where: str, second: bool) -> None:
     dim = _get(m, "dim", where)
     _get(m, "vdim", where)
     _get(m, "scale", where, float)
-    if second:
+    if m.get("softcap") is not None:
         _get(m, "softcap", where, float)
-    elif m.get("softcap") is not None:
-        raise ConfigError(f"config.json: '{where}softcap' is not part of this mixer")
     if not isinstance(m.get("v_mix", False), bool):
         raise ConfigError(f"config.json: '{where}v_mix' must be true or false, got {m.get('v_mix')!r}")
-    _rotation(m.get("rot"), where + "rot.", dim, second)
+    _rotation(m.get("rot"), where + "rot.", dim)
 
 
 def _mamba2(m, where: str) -> None:

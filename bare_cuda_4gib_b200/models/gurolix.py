@@ -33,9 +33,9 @@ def _attention(cfg: GurolixConfig, m, p: str, second: bool, v_mix) -> PartSpec:
     return PartSpec("general_attention",
                     {"hidden": cfg.width, "heads": m["heads"], "kv_heads": m["kv_heads"], "dim": m["dim"], "vdim": m["vdim"],
                      "scale": m["scale"], "eps": cfg.norm_eps, "bias": True, "qk_norm": not second,
-                     "softcap": m["softcap"] if second else None, "window": None, "v_mix": v_mix,
+                     "softcap": m.get("softcap"), "window": None, "v_mix": v_mix,
                      "position": PartSpec("rotary_halves", {"dims": rot["dims"], "base": rot["base"],
-                                                            "scaling": rot.get("scaling") if second else None})}, names)
+                                                            "scaling": rot.get("scaling")})}, names)
 
 
 def _mamba2(cfg: GurolixConfig, m, p: str) -> PartSpec:

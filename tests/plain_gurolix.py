@@ -98,7 +98,7 @@ def attention(t: Dict[str, torch.Tensor], p: str, m, h, eps, kind: str, v_first:
     if v_first is not None:
         lam = t[p + "vmix"].to(F64).reshape(())
         v = (1.0 - lam) * v + lam * v_first
-    cap = m.get("softcap") if kind == "attention_2" else None
+    cap = m.get("softcap")
     outs = []
     for head in range(H):
         g = head // (H // G)

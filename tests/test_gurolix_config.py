@@ -62,12 +62,11 @@ def test_configuration_errors_name_the_key():
         return str(e.value)
 
     assert "layers[1].mixer.kv_heads" in broken(lambda c: c["layers"][1]["mixer"].update(kv_heads=3))
-    assert "layers[1].mixer.softcap" in broken(lambda c: c["layers"][1]["mixer"].pop("softcap"))
-    assert "layers[2].mixer.softcap" in broken(lambda c: c["layers"][2]["mixer"].update(softcap=3.0))
+    assert "layers[1].mixer.softcap" in broken(lambda c: c["layers"][1]["mixer"].update(softcap=-1.0))
     assert "layers[1].mixer.rot.dims" in broken(lambda c: c["layers"][1]["mixer"]["rot"].update(dims=7))
     assert "layers[1].mixer.rot.dims" in broken(lambda c: c["layers"][1]["mixer"]["rot"].update(dims=18))
     assert "layers[1].mixer.rot.scaling.factor" in broken(lambda c: c["layers"][1]["mixer"]["rot"]["scaling"].pop("factor"))
-    assert "layers[2].mixer.rot.scaling" in broken(lambda c: c["layers"][2]["mixer"]["rot"].update(scaling={"factor": 2.0}))
+    assert "layers[2].mixer.rot.scaling.low" in broken(lambda c: c["layers"][2]["mixer"]["rot"].update(scaling={"factor": 2.0}))
     assert "layers[0].mixer.groups" in broken(lambda c: c["layers"][0]["mixer"].update(groups=3))
     assert "layers[0].mixer.norm_groups" in broken(lambda c: c["layers"][0]["mixer"].update(norm_groups=5))
     assert "layers[0].mixer.state" in broken(lambda c: c["layers"][0]["mixer"].pop("state"))

@@ -53,6 +53,8 @@ ALONE = {
     "mamba2_twice": [U.mamba2(2, 16, 16, 2, 2, 1), U.mamba2(4, 8, 8, 1, 4, 2)],
     "mamba2_norm_parts_inside_heads": [U.mamba2(2, 24, 16, 1, 3, 6)],                  # a head spans three parts of the norm
     "mamba2_part_over_two_groups": [U.mamba2(8, 8, 16, 4, 4, 2)],                      # a part's heads read two groups each
+    "mamba2_odd_sizes": [U.mamba2(3, 6, 10, 3, 3, 1)],                                # nothing lines up with 16 bytes
+    "normed_with_cap_and_rescaled_frequencies": [U.attention(2, 1, 16, 16, 16, scale=0.6)],   # (the options added below)
     "mamba2_wide_heads": [U.mamba2(2, 320, 8, 2, 2, 2)],                               # more value columns than a block has threads
     "experts_with_identity_and_groups": [U.attention(2, 1, 16, 16, 8, mlp=U.moe(5, 2, 24, identity=1, groups=(3, 2)))],
     "experts_mostly_identity": [U.mamba2(2, 8, 8, 1, 2, 1, mlp=U.moe(2, 3, 16, identity=6, groups=(4, 2)))],
@@ -80,6 +82,11 @@ def test_each_mechanism_alone(which, dtype):
     steps = H.trace_portions({"a": requests["a"]}, random.Random(1))
     got = H.Replayer(folder, dtype, 16, 96, shuffle_seed=2).run(steps)
     U.check(folder, {"a": requests["a"]}, got, dtype)
+
+
+ALONE["normed_with_cap_and_rescaled_frequencies"][0]["mixer"].update(softcap=3.0)
+ALONE["normed_with_cap_and_rescaled_frequencies"][0]["mixer"]["rot"].update(
+    scaling=dict(zip(("factor", "low", "high", "original"), SCALING)))
 
 
 def _stream():
@@ -216,7 +223,7 @@ def test_whole(name, dtype):
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_whole_in_bfloat16_with_the_routers_as_they_are(name):
     """The configurations' own routers in a bfloat16 run: most rows agree; a row behind a tie that rounding
-    decided the other way does not, so this run is judged by the share of rows only."""
+    decided the other way does not, so this run goes by the share of rows only."""
     folder, page = U.model_folder(name), U.CONFIGS[name][1]
     requests = _requests(name, 1, LENGTHS[name])
     steps = H.trace_whole(requests)
