@@ -6,6 +6,8 @@
 //   S_h <- a_h S_h + (dt_h B_g) x_h^T  (N x P, g = h / (H / G));   y_h = S_h^T C_g + D_h x_h
 //   out = rms_norm in `parts` equal parts of (y * silu(z)) * w
 //
+// (With `compact`, mamba2_operands instead leaves [x | B | C] once per token in bfloat16 with the step sizes and
+// the decays' logarithms, for the chunked walk on the tensor cores of mamba2_chunked.cu.)
 // mamba2_operands makes the scan's float32 operands from the projection (decay per token and head,
 // k = B of the head's group, v = dt * x, q = C of the head's group) and keeps x for the D term; the scan
 // (linear_attention.cu) walks the state; mamba2_finish adds D x, gates, norms and rounds.  The
@@ -30,7 +32,7 @@ mamba2_operands_kernel(const T* __restrict__ u, long long u_stride, const float*
                        float* __restrict__ kf, float* __restrict__ vf, float* __restrict__ xc, float* __restrict__ decay,
                        const int32_t* __restrict__ positions, const int32_t* __restrict__ row_seq,
                        const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ seq_q_start, int H, int P, int N,
-                       int G) {
+                       int G, __nv_bfloat16* __restrict__ compact, float* __restrict__ dt_out, float* __restrict__ la_out) {
   pdl_launch_dependents();
   extern __shared__ float sm[];      // C conv channels, then H step sizes
   const int inner = H * P, C = inner + 2 * G * N;
@@ -47,7 +49,12 @@ mamba2_operands_kernel(const T* __restrict__ u, long long u_stride, const float*
   for (int h = threadIdx.x; h < H; h += blockDim.x) {
     const float dt = softplus_f(to_float(row[inner + C + h]) + dt_bias[h]);
     dts[h] = dt;
-    decay[(long long)t * H + h] = expf(-expf(a_log[h]) * dt);
+    if (compact) {      // the chunked walk takes the step size and the decay's logarithm
+      dt_out[(long long)t * H + h] = dt;
+      la_out[(long long)t * H + h] = -expf(a_log[h]) * dt;
+    } else {
+      decay[(long long)t * H + h] = expf(-expf(a_log[h]) * dt);
+    }
   }
   const bool inside = p - hist >= p0;      // all taps inside the step's own rows
   for (int c = threadIdx.x; c < C; c += blockDim.x) {
@@ -68,6 +75,14 @@ mamba2_operands_kernel(const T* __restrict__ u, long long u_stride, const float*
     ys[c] = silu_f(y);
   }
   __syncthreads();
+  if (compact) {
+    // [x | B | C] once, rounded to bfloat16 (activations of the convolution), for the chunked walk
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+      compact[(long long)t * C + c] = __float2bfloat16_rn(ys[c]);
+      if (c < inner) xc[(long long)t * inner + c] = ys[c];
+    }
+    return;
+  }
   for (int c = threadIdx.x; c < inner; c += blockDim.x) {
     const float x = ys[c];
     xc[(long long)t * inner + c] = x;
@@ -85,7 +100,8 @@ extern "C" int llm_mamba2_operands(const void* u, int dtype, long long u_stride,
                                    int taps, const float* ring, const float* dt_bias, const float* a_log, float* qf,
                                    float* kf, float* vf, float* xc, float* decay, const int32_t* positions,
                                    const int32_t* row_seq, const int32_t* seq_slot, const int32_t* seq_q_start,
-                                   int n_tokens, int H, int P, int N, int G, cudaStream_t stream) {
+                                   int n_tokens, int H, int P, int N, int G, void* compact, float* dt_out, float* la_out,
+                                   cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   LLM_HOST_CHECK(taps >= 1 && H >= 1 && G >= 1 && H % G == 0 && P >= 1 && N >= 1, ERR_BAD_SIZE);
   const size_t smem = (size_t)(H * P + 2 * G * N + H) * sizeof(float);
@@ -95,7 +111,8 @@ extern "C" int llm_mamba2_operands(const void* u, int dtype, long long u_stride,
     if (smem > 48 * 1024)                                                                                           \
       cudaFuncSetAttribute(mamba2_operands_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);      \
     launch_kernel(mamba2_operands_kernel<T>, n_tokens, 256, smem, stream, (const T*)u, u_stride, conv_w, conv_b, taps, \
-                  ring, dt_bias, a_log, qf, kf, vf, xc, decay, positions, row_seq, seq_slot, seq_q_start, H, P, N, G); \
+                  ring, dt_bias, a_log, qf, kf, vf, xc, decay, positions, row_seq, seq_slot, seq_q_start, H, P, N, G, \
+                  (__nv_bfloat16*)compact, dt_out, la_out);                                                         \
   } while (0)
   if (dtype == DT_F32) LAUNCH(float);
   else if (dtype == DT_BF16) LAUNCH(__nv_bfloat16);

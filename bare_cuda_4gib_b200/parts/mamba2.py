@@ -11,7 +11,9 @@ weight, and the output projection.  A request keeps S as a float32 state [heads,
 convolution's last inputs as a second one (a ring of `taps` entries by position); the walk over a
 step's tokens is the engine's state scan (`kernels.linear_attention.scan`) with one decay per token and
 head, fed with float32 operands; the kernels of csrc/mamba2.cu come before and after it.  In a step of one
-token per request one kernel with a block per (request, head) stands for operands, ring and scan.
+token per request one kernel with a block per (request, head) stands for operands, ring and scan.  In
+bfloat16 steps with a portion of 32 tokens or more (state and value sizes that are multiples of 16) the
+recurrence runs in chunks of 64 tokens on the tensor cores (csrc/mamba2_chunked.cu) instead of the scan.
 
 params: `hidden`, `heads`, `vdim`, `state`, `groups`, `taps`, `norm_groups`, `eps`.
 tensors: `in` [2 * heads * vdim + 2 * groups * state + heads, hidden], `conv` [channels, taps], `conv_bias`
@@ -77,6 +79,9 @@ class Mamba2(Part):
         self.conv_w, self.conv_b = f(t["conv"]), f(t["conv_bias"])
         self.dt_bias, self.a_log, self.d_skip, self.norm_w = f(t["dt_bias"]), f(t["A_log"]), f(t["D"]), f(t["norm"])
         self.one_step = device.type == "cuda" and MK.step_takes(self.heads, self.vdim, self.state, self.groups)
+        self.chunked = device.type == "cuda" and dtype == torch.bfloat16 and MK.chunked_takes(self.state, self.vdim)
+        if self.chunked:
+            MK.chunked_lib(self.state, self.vdim)      # compiled with the model, not at its first long portion
 
     def forward(self, ctx, call, h):
         n, H, P, N = ctx.n_tokens, self.heads, self.vdim, self.state
@@ -89,6 +94,18 @@ class Mamba2(Part):
         if ctx.max_q_len == 1 and self.one_step:
             MK.step(ctx, u, self.conv_w, self.conv_b, ring, self.dt_bias, self.a_log, state, scanned, xc, H, P, N,
                     self.groups, call.writes_cache)
+            MK.finish(ctx, scanned, xc, self.d_skip, u[:, : self.inner], self.norm_w, out, P, self.norm_groups, self.eps)
+            return self.o.forward(ctx, out, n, torch.float32, "mixer_out", allow_partials=True)
+        if ctx.dtype == torch.bfloat16 and self.chunked and ctx.max_q_len >= MK.CHUNKED_MIN_TOKENS and ctx.use_fast_attention:
+            # long portions of a bfloat16 step: the recurrence in chunks on the tensor cores
+            compact = ctx.ws.get("mamba2_compact", (n, self.conv_channels), torch.bfloat16)
+            dt = ctx.ws.get("mamba2_dt", (n, H), f32)
+            la = ctx.ws.get("mamba2_la", (n, H), f32)
+            MK.operands(ctx, u, self.conv_w, self.conv_b, ring, self.dt_bias, self.a_log, None, None, None, xc, None, H, P, N,
+                        self.groups, compact, dt, la)
+            if call.writes_cache:
+                MK.ring_write(ctx, u[:, self.inner: self.inner + self.conv_channels], ring, self.taps, self.conv_channels)
+            MK.chunked(ctx, compact, dt, la, state, scanned, H, P, N, self.groups)
             MK.finish(ctx, scanned, xc, self.d_skip, u[:, : self.inner], self.norm_w, out, P, self.norm_groups, self.eps)
             return self.o.forward(ctx, out, n, torch.float32, "mixer_out", allow_partials=True)
         qf = ctx.ws.get("mamba2_q", (n, H * N), f32)

@@ -53,6 +53,8 @@ ALONE = {
     "mamba2_twice": [U.mamba2(2, 16, 16, 2, 2, 1), U.mamba2(4, 8, 8, 1, 4, 2)],
     "mamba2_norm_parts_inside_heads": [U.mamba2(2, 24, 16, 1, 3, 6)],                  # a head spans three parts of the norm
     "mamba2_part_over_two_groups": [U.mamba2(8, 8, 16, 4, 4, 2)],                      # a part's heads read two groups each
+    "mamba2_tensor_core_sizes": [U.mamba2(4, 32, 48, 2, 4, 2)],                        # three row tiles of state for four warps
+    "mamba2_tensor_core_sizes_wide": [U.mamba2(2, 64, 128, 1, 4, 1)],
     "mamba2_odd_sizes": [U.mamba2(3, 6, 10, 3, 3, 1)],                                # nothing lines up with 16 bytes
     "normed_with_cap_and_rescaled_frequencies": [U.attention(2, 1, 16, 16, 16, scale=0.6)],   # (the options added below)
     "mamba2_wide_heads": [U.mamba2(2, 320, 8, 2, 2, 2)],                               # more value columns than a block has threads
@@ -206,6 +208,62 @@ def test_gated_step_kernel_alone(rows, width):
     GS.step(res, None, nxt.cuda(), out, 1e-6, 3, index)
     assert torch.equal(res.cpu(), x)
     assert H.row_error(out, (unit(x.to(d), 1e-6) * nxt.to(d))[index.cpu().long()]) < 1e-2
+
+
+@pytest.mark.parametrize("heads,vdim,state,groups", [(4, 64, 128, 2), (3, 16, 16, 3), (2, 32, 48, 1), (2, 96, 32, 2)])
+def test_chunked_walk_against_the_scan(heads, vdim, state, groups):
+    """The recurrence in chunks on the tensor cores against the float32 scan on the same inputs: three requests of
+    unequal length (one shorter than a chunk, one that ends inside its fourth), states that are not empty."""
+    from bare_cuda_4gib_b200.engine.step import Workspace
+    from bare_cuda_4gib_b200.kernels import linear_attention as LA, mamba2 as MK
+    g = torch.Generator().manual_seed(heads)
+    lengths, taps = [200, 37, 64], 3
+    n, inner = sum(lengths), heads * vdim
+    C = inner + 2 * groups * state
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+
+    class Ctx:
+        stream = torch.cuda.current_stream().cuda_stream
+        dtype = torch.bfloat16
+        n_tokens, n_seqs, max_q_len = n, len(lengths), max(lengths)
+        positions = i32([p for q in lengths for p in range(q)])
+        row_seq = i32([s for s, q in enumerate(lengths) for _ in range(q)])
+        seq_slot = i32([2, 0, 1])
+        seq_q_start = i32([0, 200, 237])
+        seq_q_len = i32(lengths)
+        seq_kv_len = i32(lengths)
+        ws = Workspace(torch.device("cuda"), n)
+
+    u = torch.randn(n, inner + C + heads, generator=g).to(torch.bfloat16).cuda()
+    conv_w = (torch.randn(C, taps, generator=g) / taps ** 0.5).cuda()
+    conv_b = (0.2 * torch.randn(C, generator=g)).cuda()
+    ring = torch.zeros(4, taps, C, device="cuda")
+    dt_bias, a_log = torch.randn(heads, generator=g).cuda(), (0.5 * torch.randn(heads, generator=g) - 1.0).cuda()
+    start = torch.randn(4, heads, state, vdim, generator=g).cuda()
+    f32 = dict(dtype=torch.float32, device="cuda")
+    qf, kf = torch.empty(n, heads * state, **f32), torch.empty(n, heads * state, **f32)
+    vf, xc, decay = torch.empty(n, inner, **f32), torch.empty(n, inner, **f32), torch.empty(n, heads, **f32)
+    MK.operands(Ctx, u, conv_w, conv_b, ring, dt_bias, a_log, qf, kf, vf, xc, decay, heads, vdim, state, groups)
+    compact = torch.empty(n, C, dtype=torch.bfloat16, device="cuda")
+    dt, la = torch.empty(n, heads, **f32), torch.empty(n, heads, **f32)
+    xc2 = torch.empty(n, inner, **f32)
+    MK.operands(Ctx, u, conv_w, conv_b, ring, dt_bias, a_log, None, None, None, xc2, None, heads, vdim, state, groups, compact, dt, la)
+    r = lambda t: t.to(torch.bfloat16).float()
+    assert torch.equal(xc2, xc) and torch.equal(compact[:, :inner].float(), r(xc))
+    assert torch.allclose(torch.exp(la), decay, rtol=1e-6) and torch.allclose(dt.repeat_interleave(vdim, 1) * xc, vf, rtol=1e-6)
+    # the scan on what the chunked walk gets: B, C and x rounded to bfloat16, step sizes and decays as they are
+    want_state, want = start.clone(), torch.empty(n, inner, **f32)
+
+    class F32(Ctx):
+        dtype = torch.float32
+    LA.scan(F32, r(qf), r(kf), dt.repeat_interleave(vdim, 1) * r(xc), decay, "token", want_state, want, heads, state, vdim)
+    got_state, got = start.clone(), torch.full((n, inner), float("nan"), **f32)
+    MK.chunked(Ctx, compact, dt, la, got_state, got, heads, vdim, state, groups)
+    torch.cuda.synchronize()
+    assert torch.equal(got_state[3], start[3])                    # a slot that no request of the step holds
+    scale = float(want.abs().max())
+    assert float((got - want).abs().max()) < 2e-3 * scale, float((got - want).abs().max()) / scale
+    assert float((got_state - want_state).abs().max()) < 2e-3 * float(want_state.abs().max())
 
 
 # ------------------------------------------------------------------ every cutting, two configs
