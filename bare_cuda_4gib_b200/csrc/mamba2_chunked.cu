@@ -14,7 +14,8 @@
 // products, so it keeps 16 significant bits.  The state lives in registers across chunks (float32) and in
 // shared memory as such a pair for the product with C.
 //
-// Built per model with -DSSD_N (state size) and -DSSD_P (value size of a head), multiples of 16.
+// Built per model with -DSSD_N (state size) and -DSSD_P (value size of a head), multiples of 16, and
+// optionally -DSSD_PC (value columns of a block).
 
 #include "common.cuh"
 
@@ -33,7 +34,12 @@ constexpr int N = SSD_N, P = SSD_P;
 static_assert(N % 16 == 0 && N >= 16 && N <= 256, "SSD_N must be a multiple of 16 up to 256");
 static_assert(P % 16 == 0 && P >= 16, "SSD_P must be a multiple of 16");
 constexpr int L = 64;                         // tokens of a chunk
-constexpr int PC = P % 32 == 0 ? 32 : 16;     // value columns of a block
+#ifndef SSD_PC
+#define SSD_PC (SSD_P % 32 == 0 ? 32 : 16)
+#endif
+constexpr int PC = SSD_PC;                    // value columns of a block: 32, or 16 where the model's heads alone
+                                              // would leave most SMs without a block
+static_assert((PC == 16 || PC == 32) && P % PC == 0, "SSD_PC must be 16 or 32 and divide SSD_P");
 constexpr int LDN = N + 8, LDP = PC + 8;      // padded rows (conflict-free ldmatrix)
 constexpr int WARPS = 4, THREADS = WARPS * 32;
 constexpr int MT_N = N / 16;                  // row tiles of the state
@@ -155,12 +161,16 @@ __global__ void __launch_bounds__(THREADS) mamba2_chunked_kernel(SsdArgs a) {
       cum[r] = r < count ? a.la[(row0 + r) * H + h] : 0.0f;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      float run = 0.0f;
-      for (int r = 0; r < L; ++r) {
-        run += cum[r];
-        cum[r] = run;
+    if (warp == 0) {      // the running sum over the chunk's 64 tokens: a lane takes two neighbours
+      const float v0 = cum[2 * lane], v1 = cum[2 * lane + 1];
+      float run = v0 + v1;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, run, o);
+        if (lane >= o) run += up;
       }
+      cum[2 * lane] = run - v1;
+      cum[2 * lane + 1] = run;
     }
     __syncthreads();
     const float cum_last = cum[L - 1];
@@ -315,11 +325,7 @@ constexpr size_t SMEM = (size_t)(2 * L * LDN + 3 * L * LDP + 2 * N * LDP) * 2 + 
 
 }  // namespace
 
-extern "C" int llm_mamba2_chunked_sizes(int* n, int* p) {
-  *n = N;
-  *p = P;
-  return 0;
-}
+extern "C" int llm_mamba2_chunked_columns() { return PC; }
 
 extern "C" int llm_mamba2_chunked(const void* x, const void* b, const void* c, long long in_stride, const float* dt,
                                   const float* la, float* state,

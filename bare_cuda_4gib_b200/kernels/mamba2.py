@@ -111,19 +111,27 @@ def chunked_takes(state: int, vdim: int) -> bool:
     return state % 16 == 0 and 16 <= state <= 256 and vdim % 16 == 0 and 16 <= vdim <= 1024
 
 
-def chunked_lib(state: int, vdim: int):
-    l = _chunked_libs.get((state, vdim))
+def chunked_columns(heads: int, vdim: int) -> int:
+    """Value columns of a block: 32, or 16 where one request's blocks (heads x vdim / 32) would not reach the
+    number of SMs, so that a single long prompt still puts a block on every SM."""
+    from .lib import sm_count
+    return 32 if vdim % 32 == 0 and heads * (vdim // 32) >= sm_count() else 16
+
+
+def chunked_lib(state: int, vdim: int, columns: int = 0):
+    columns = columns or (32 if vdim % 32 == 0 else 16)
+    l = _chunked_libs.get((state, vdim, columns))
     if l is None:
-        l = build.load_library("mamba2_chunked.cu", (f"-DSSD_N={state}", f"-DSSD_P={vdim}"))
+        l = build.load_library("mamba2_chunked.cu", (f"-DSSD_N={state}", f"-DSSD_P={vdim}", f"-DSSD_PC={columns}"))
         P, I, L = c_void_p, c_int, c_longlong
         l.llm_mamba2_chunked.argtypes = [P, P, P, L, P, P, P, P, P, P, P, I, I, I, I, I, P]
         l.llm_mamba2_chunked.restype = c_int
-        _chunked_libs[(state, vdim)] = l
+        _chunked_libs[(state, vdim, columns)] = l
     return l
 
 
 def chunked(ctx, compact: torch.Tensor, dt: torch.Tensor, la: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
-            heads: int, vdim: int, state_size: int, groups: int) -> None:
+            heads: int, vdim: int, state_size: int, groups: int, columns: int = 0) -> None:
     """The recurrence of every request's portion in chunks of 64 tokens on the tensor cores: compact
     [rows, x | B | C] bfloat16, dt and la (the decays' logarithms) float32 [rows, heads]; the states
     [slots, heads, state, vdim] float32 are read and left as after the portions' last tokens; out [rows, heads *
@@ -133,7 +141,7 @@ def chunked(ctx, compact: torch.Tensor, dt: torch.Tensor, la: torch.Tensor, stat
     if compact.dtype != torch.bfloat16 or state.dtype != torch.float32 or out.dtype != torch.float32 or not out.is_contiguous():
         raise TypeError("mamba2 chunked: element types or layout not as the kernel needs")
     base, esize = compact.data_ptr(), 2
-    _check(chunked_lib(state_size, vdim).llm_mamba2_chunked(
+    _check(chunked_lib(state_size, vdim, columns).llm_mamba2_chunked(
         base, base + inner * esize, base + (inner + groups * state_size) * esize, compact.stride(0), dt.data_ptr(),
         la.data_ptr(), state.data_ptr(), out.data_ptr(), ctx.seq_slot.data_ptr(), ctx.seq_q_start.data_ptr(),
         ctx.seq_q_len.data_ptr(), ctx.n_seqs, heads, groups, state_size, vdim, ctx.stream), "mamba2_chunked")

@@ -11,7 +11,8 @@ def all_libraries():
             ("linear_attention.cu", ()), ("biased_attention.cu", ()), ("sandwich_norm.cu", ()), ("head_prepare.cu", ()),
             ("latent_attention.cu", ()), ("mlstm.cu", ()), ("diff_attention.cu", ()), ("moe.cu", ()),
             ("gated_sandwich.cu", ()), ("mamba2.cu", ()),
-            ("mamba2_chunked.cu", ("-DSSD_N=128", "-DSSD_P=64")), ("mamba2_chunked.cu", ("-DSSD_N=16", "-DSSD_P=16"))]
+            ("mamba2_chunked.cu", ("-DSSD_N=128", "-DSSD_P=64", "-DSSD_PC=16")),
+            ("mamba2_chunked.cu", ("-DSSD_N=128", "-DSSD_P=64", "-DSSD_PC=32"))]
     jobs += [("gemm_tcgen05.cu", ("-DGLU_GELU_TANH",)), ("gemv_fused.cu", ("-DGLU_GELU_TANH",)),
              ("gemm_tcgen05.cu", ("-DGROUPED_UP_RELU2",))]
     jobs += [("attention_mma.cu", (f"-DHEAD_DIM={d}",)) for d in ATTENTION_HEAD_DIMS]

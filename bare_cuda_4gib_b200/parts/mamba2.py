@@ -81,7 +81,8 @@ class Mamba2(Part):
         self.one_step = device.type == "cuda" and MK.step_takes(self.heads, self.vdim, self.state, self.groups)
         self.chunked = device.type == "cuda" and dtype == torch.bfloat16 and MK.chunked_takes(self.state, self.vdim)
         if self.chunked:
-            MK.chunked_lib(self.state, self.vdim)      # compiled with the model, not at its first long portion
+            self.chunk_columns = MK.chunked_columns(self.heads, self.vdim)
+            MK.chunked_lib(self.state, self.vdim, self.chunk_columns)      # compiled with the model, not at its first long portion
 
     def forward(self, ctx, call, h):
         n, H, P, N = ctx.n_tokens, self.heads, self.vdim, self.state
@@ -105,7 +106,7 @@ class Mamba2(Part):
                         self.groups, compact, dt, la)
             if call.writes_cache:
                 MK.ring_write(ctx, u[:, self.inner: self.inner + self.conv_channels], ring, self.taps, self.conv_channels)
-            MK.chunked(ctx, compact, dt, la, state, scanned, H, P, N, self.groups)
+            MK.chunked(ctx, compact, dt, la, state, scanned, H, P, N, self.groups, self.chunk_columns)
             MK.finish(ctx, scanned, xc, self.d_skip, u[:, : self.inner], self.norm_w, out, P, self.norm_groups, self.eps)
             return self.o.forward(ctx, out, n, torch.float32, "mixer_out", allow_partials=True)
         qf = ctx.ws.get("mamba2_q", (n, H * N), f32)

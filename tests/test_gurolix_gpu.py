@@ -257,13 +257,14 @@ def test_chunked_walk_against_the_scan(heads, vdim, state, groups):
     class F32(Ctx):
         dtype = torch.float32
     LA.scan(F32, r(qf), r(kf), dt.repeat_interleave(vdim, 1) * r(xc), decay, "token", want_state, want, heads, state, vdim)
-    got_state, got = start.clone(), torch.full((n, inner), float("nan"), **f32)
-    MK.chunked(Ctx, compact, dt, la, got_state, got, heads, vdim, state, groups)
-    torch.cuda.synchronize()
-    assert torch.equal(got_state[3], start[3])                    # a slot that no request of the step holds
-    scale = float(want.abs().max())
-    assert float((got - want).abs().max()) < 2e-3 * scale, float((got - want).abs().max()) / scale
-    assert float((got_state - want_state).abs().max()) < 2e-3 * float(want_state.abs().max())
+    for columns in (0, 16):      # value columns of a block: the default for the size, and the narrow form
+        got_state, got = start.clone(), torch.full((n, inner), float("nan"), **f32)
+        MK.chunked(Ctx, compact, dt, la, got_state, got, heads, vdim, state, groups, columns)
+        torch.cuda.synchronize()
+        assert torch.equal(got_state[3], start[3])                    # a slot that no request of the step holds
+        scale = float(want.abs().max())
+        assert float((got - want).abs().max()) < 2e-3 * scale, float((got - want).abs().max()) / scale
+        assert float((got_state - want_state).abs().max()) < 2e-3 * float(want_state.abs().max())
 
 
 # ------------------------------------------------------------------ every cutting, two configs
