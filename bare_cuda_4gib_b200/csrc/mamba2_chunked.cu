@@ -12,7 +12,8 @@
 // factor has to enter a product's operand (the masked weights (C_i . B_j) exp(..) dt_j, x times its decay to
 // the chunk's end, the carried state) the operand is a bfloat16 number plus what its rounding left, two
 // products, so it keeps 16 significant bits.  The state lives in registers across chunks (float32) and in
-// shared memory as such a pair for the product with C.
+// shared memory as such a pair for the product with C.  A chunk's tiles arrive by cp.async while the chunk
+// before them is being multiplied (two sets of stages).
 //
 // Built per model with -DSSD_N (state size) and -DSSD_P (value size of a head), multiples of 16, and
 // optionally -DSSD_PC (value columns of a block).
@@ -47,6 +48,16 @@ constexpr int MTW = (MT_N + WARPS - 1) / WARPS;   // of which a warp owns at mos
 constexpr int NT = PC / 8;                    // column tiles of a block's columns
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+// 16 (or 4) bytes from global to shared memory without passing through registers; `valid` false fills zeros
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void* dst, const void* src, bool valid) {
+  const int bytes = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -90,15 +101,17 @@ struct SsdArgs {
 
 __global__ void __launch_bounds__(THREADS) mamba2_chunked_kernel(SsdArgs a) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  __nv_bfloat16* Bs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [L][LDN]
-  __nv_bfloat16* Cs = Bs + L * LDN;                                 // [L][LDN]
-  __nv_bfloat16* Xs = Cs + L * LDN;                                 // [L][LDP]  x
-  __nv_bfloat16* Xh = Xs + L * LDP;                                 // [L][LDP]  x times its decay to the chunk's end and dt: rounded ...
+  // two sets of a chunk's tiles: the next chunk's arrive by cp.async while this chunk's products run
+  __nv_bfloat16* Bs0 = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [2][L][LDN]
+  __nv_bfloat16* Cs0 = Bs0 + 2 * L * LDN;                           // [2][L][LDN]
+  __nv_bfloat16* Xs0 = Cs0 + 2 * L * LDN;                           // [2][L][LDP]  x
+  __nv_bfloat16* Xh = Xs0 + 2 * L * LDP;                            // [L][LDP]  x times its decay to the chunk's end and dt: rounded ...
   __nv_bfloat16* Xl = Xh + L * LDP;                                 // ... and what the rounding left
   __nv_bfloat16* Sh = Xl + L * LDP;                                 // [N][LDP]  the state at the chunk's start, likewise
   __nv_bfloat16* Sl = Sh + N * LDP;
   float* cum = reinterpret_cast<float*>(Sl + N * LDP);              // [L]
-  float* dts = cum + L;                                             // [L]
+  float* dts0 = cum + L;                                            // [2][L] step sizes
+  float* las0 = dts0 + 2 * L;                                       // [2][L] logarithms of the decays
 
   pdl_launch_dependents();
   pdl_wait();
@@ -134,35 +147,51 @@ __global__ void __launch_bounds__(THREADS) mamba2_chunked_kernel(SsdArgs a) {
   }
 
   const int n_chunks = (q_len + L - 1) / L;
+  constexpr int CN = N / 8, CP = PC / 8;
+  // requests chunk `ch`'s B, C, x (rows past the portion's end are zero), step sizes and decays, and closes one group
+  auto load_chunk = [&](int ch) {
+    if (ch < n_chunks) {
+      const int st = ch & 1, count = min(L, q_len - ch * L);
+      const long long row0 = q_start + (long long)ch * L;
+      __nv_bfloat16* Bd = Bs0 + st * L * LDN;
+      __nv_bfloat16* Cd = Cs0 + st * L * LDN;
+      __nv_bfloat16* Xd = Xs0 + st * L * LDP;
+      for (int i = threadIdx.x; i < L * CN; i += THREADS) {
+        const int r = i / CN, c8 = i % CN;
+        const bool valid = r < count;
+        const long long src = valid ? (row0 + r) * bc_stride + g * N + c8 * 8 : 0;
+        cp_async16(Bd + r * LDN + c8 * 8, a.b + src, valid);
+        cp_async16(Cd + r * LDN + c8 * 8, a.c + src, valid);
+      }
+      for (int i = threadIdx.x; i < L * CP; i += THREADS) {
+        const int r = i / CP, c8 = i % CP;
+        const bool valid = r < count;
+        cp_async16(Xd + r * LDP + c8 * 8, a.x + (valid ? (row0 + r) * x_stride + h * P + col0 + c8 * 8 : 0), valid);
+      }
+      if (threadIdx.x < L) {
+        const int r = threadIdx.x;
+        const bool valid = r < count;
+        const long long src = valid ? (row0 + r) * H + h : 0;
+        cp_async4(dts0 + st * L + r, a.dt + src, valid);
+        cp_async4(las0 + st * L + r, a.la + src, valid);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  load_chunk(0);
   for (int ch = 0; ch < n_chunks; ++ch) {
     const int t0 = ch * L, count = min(L, q_len - t0);
     const long long row0 = q_start + t0;
-    // ---- the chunk's B, C, x (rows past the portion's end are zero), step sizes and the running sum of la
-    constexpr int CN = N / 8, CP = PC / 8;
-    for (int i = threadIdx.x; i < L * CN; i += THREADS) {
-      const int r = i / CN, c8 = i % CN;
-      uint4 vb = make_uint4(0, 0, 0, 0), vc = vb;
-      if (r < count) {
-        vb = *reinterpret_cast<const uint4*>(a.b + (row0 + r) * bc_stride + g * N + c8 * 8);
-        vc = *reinterpret_cast<const uint4*>(a.c + (row0 + r) * bc_stride + g * N + c8 * 8);
-      }
-      *reinterpret_cast<uint4*>(Bs + r * LDN + c8 * 8) = vb;
-      *reinterpret_cast<uint4*>(Cs + r * LDN + c8 * 8) = vc;
-    }
-    for (int i = threadIdx.x; i < L * CP; i += THREADS) {
-      const int r = i / CP, c8 = i % CP;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (r < count) v = *reinterpret_cast<const uint4*>(a.x + (row0 + r) * x_stride + h * P + col0 + c8 * 8);
-      *reinterpret_cast<uint4*>(Xs + r * LDP + c8 * 8) = v;
-    }
-    if (threadIdx.x < L) {
-      const int r = threadIdx.x;
-      dts[r] = r < count ? a.dt[(row0 + r) * H + h] : 0.0f;
-      cum[r] = r < count ? a.la[(row0 + r) * H + h] : 0.0f;
-    }
-    __syncthreads();
+    const __nv_bfloat16* Bs = Bs0 + (ch & 1) * L * LDN;
+    const __nv_bfloat16* Cs = Cs0 + (ch & 1) * L * LDN;
+    const __nv_bfloat16* Xs = Xs0 + (ch & 1) * L * LDP;
+    const float* dts = dts0 + (ch & 1) * L;
+    const float* las = las0 + (ch & 1) * L;
+    load_chunk(ch + 1);      // into the other set, which every warp left at the last chunk's end
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();         // chunk `ch` has landed
     if (warp == 0) {      // the running sum over the chunk's 64 tokens: a lane takes two neighbours
-      const float v0 = cum[2 * lane], v1 = cum[2 * lane + 1];
+      const float v0 = las[2 * lane], v1 = las[2 * lane + 1];
       float run = v0 + v1;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -305,7 +334,7 @@ __global__ void __launch_bounds__(THREADS) mamba2_chunked_kernel(SsdArgs a) {
           Sl[n * LDP + col] = __float2bfloat16_rn(v - rounded(v));
         }
     }
-    // (the next chunk's loads are followed by a barrier before anything reads the state or the tiles)
+    // (the next chunk's barriers come before anything reads the state again)
   }
 #pragma unroll
   for (int i = 0; i < MTW; ++i) {
@@ -321,7 +350,7 @@ __global__ void __launch_bounds__(THREADS) mamba2_chunked_kernel(SsdArgs a) {
   }
 }
 
-constexpr size_t SMEM = (size_t)(2 * L * LDN + 3 * L * LDP + 2 * N * LDP) * 2 + 2 * L * 4;
+constexpr size_t SMEM = (size_t)(4 * L * LDN + 4 * L * LDP + 2 * N * LDP) * 2 + 5 * L * 4;
 
 }  // namespace
 
