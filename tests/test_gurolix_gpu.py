@@ -91,13 +91,29 @@ ALONE["normed_with_cap_and_rescaled_frequencies"][0]["mixer"]["rot"].update(
     scaling=dict(zip(("factor", "low", "high", "original"), SCALING)))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_width_that_no_fast_kernel_takes(dtype):
+    """Width 50: no product, norm or copy in pieces of 16 bytes fits; every part takes its entry-by-entry form."""
+    layers = [U.attention_2(2, 1, 16, 16, 8, 4.0, SCALING, scale=0.4, v_mix=True, mlp=U.moe(3, 2, 8, identity=1, groups=(2, 1))),
+              U.mamba2(2, 16, 16, 1, 2, 1, mlp=U.moe(2, 1, 12)), U.attention(3, 1, 32, 16, 16, v_mix=True)]
+    if dtype == "bfloat16":
+        layers = U.every_expert_chosen({"layers": layers})["layers"]
+    folder, cfg = _model(f"width50-{dtype}", layers, 17, width=50, vocab=37)
+    rng = random.Random(4)
+    requests = {"a": U.clear_ids(folder, rng, 70, 37), "b": U.clear_ids(folder, rng, 3, 37)}
+    got = H.Replayer(folder, dtype, 16, 96).run(H.trace_whole(requests))
+    U.check(folder, requests, got, dtype)
+    got = H.Replayer(folder, dtype, 16, 96, shuffle_seed=3).run(H.trace_decode_tail({"a": requests["a"]}, 20))
+    U.check(folder, {"a": requests["a"]}, got, dtype, expect_all=False)
+
+
 def _stream():
     class Ctx:
         stream = torch.cuda.current_stream().cuda_stream
     return Ctx
 
 
-@pytest.mark.parametrize("n,experts,identity,top,groups,keep", [(70, 5, 1, 2, 3, 2), (9, 12, 4, 4, 4, 3), (300, 3, 0, 1, 1, 1),
+@pytest.mark.parametrize("n,experts,identity,top,groups,keep", [(70, 5, 1, 2, 3, 2), (9, 10, 5, 3, 5, 2), (300, 3, 0, 1, 1, 1),
                                                                 (40, 30, 3, 3, 11, 4), (5, 2, 6, 3, 4, 2)])
 def test_router_with_correction_groups_and_identity(n, experts, identity, top, groups, keep):
     from bare_cuda_4gib_b200.kernels import moe as M
